@@ -1,0 +1,80 @@
+"""Build libb200wmma.so in-tree with nvcc for sm_100a.
+
+The shared library is the product: every Python entry point in this package goes through it by
+ctypes and raises if it is missing.  nvcc cross-compiles without a GPU, so this runs anywhere the
+CUDA toolkit is installed.
+"""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+PKG_DIR = Path(__file__).resolve().parent
+CSRC = PKG_DIR / "csrc"
+INCLUDE = PKG_DIR.parent / "include"
+BUILD_DIR = PKG_DIR / "build"
+LIB_PATH = PKG_DIR / "libb200wmma.so"
+
+SOURCES = ["api.cu", "gemm_sm100.cu", "gemm_simple.cu", "wmma_unit.cu"]
+HEADERS = ["ptx_sm100.cuh", "gemm_sm100.cuh", "internal.h", "rng.cuh"]
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a",
+    "-O3", "-std=c++17", "-lineinfo",
+    "-Xcompiler", "-fPIC",
+    "--expt-relaxed-constexpr",
+]
+
+
+def find_nvcc() -> str:
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(nvcc):
+        raise RuntimeError("nvcc not found: the CUDA toolkit is needed to build libb200wmma.so")
+    return nvcc
+
+
+def _stale(target: Path, deps: list[Path]) -> bool:
+    if not target.exists():
+        return True
+    t = target.stat().st_mtime
+    return any(d.stat().st_mtime > t for d in deps)
+
+
+def build(force: bool = False, verbose: bool = False) -> Path:
+    """Compile every .cu under csrc/ and link libb200wmma.so next to this file."""
+    nvcc = find_nvcc()
+    BUILD_DIR.mkdir(exist_ok=True)
+    header_deps = [CSRC / h for h in HEADERS] + [INCLUDE / "b200wmma.h"]
+    jobs = []
+    for src in SOURCES:
+        obj = BUILD_DIR / (src + ".o")
+        if force or _stale(obj, [CSRC / src] + header_deps):
+            cmd = [nvcc, *NVCC_FLAGS, "-I", str(INCLUDE), "-c", str(CSRC / src), "-o", str(obj)]
+            if verbose:
+                cmd.insert(1, "-Xptxas=-v")
+            jobs.append(cmd)
+
+    def run(cmd):
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError("nvcc failed:\n" + " ".join(cmd) + "\n" + r.stdout + r.stderr)
+        return r.stdout + r.stderr
+
+    if jobs:
+        with ThreadPoolExecutor(max_workers=min(len(jobs), os.cpu_count() or 1)) as ex:
+            for out in ex.map(run, jobs):
+                if verbose and out:
+                    print(out)
+    objs = [BUILD_DIR / (s + ".o") for s in SOURCES]
+    if force or jobs or _stale(LIB_PATH, objs):
+        run([nvcc, "-Wno-deprecated-gpu-targets", "-shared", "-o", str(LIB_PATH), *map(str, objs), "-lcudart"])
+    return LIB_PATH
+
+
+if __name__ == "__main__":
+    path = build(force="--force" in sys.argv, verbose="-v" in sys.argv)
+    print(path)

@@ -1,0 +1,388 @@
+// C ABI of libb200wmma.so: handle, errors, options, GEMM dispatch, host-buffer path, memory.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstring>
+#include <string>
+
+#include "internal.h"
+#include "ptx_sm100.cuh"
+
+namespace b200 {
+
+// One warp waits on an mbarrier that nothing ever arrives on: exercises the bounded-wait path
+// (budget expiry -> status word -> clean exit) without any fault, trap or endless loop.
+__global__ void bounded_wait_selftest_kernel(int* status, unsigned long long budget_ns) {
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(smem_u32(&bar), 1);
+        fence_mbar_init();
+    }
+    __syncthreads();
+    WaitCtx wc{&abort_flag, status, budget_ns};
+    mbar_wait(smem_u32(&bar), 0, wc, kWaitSelftest);
+}
+
+static thread_local std::string g_last_error;
+
+void set_error(const std::string& msg) { g_last_error = msg; }
+int fail(int status, const std::string& msg) {
+    g_last_error = msg;
+    return status;
+}
+int cuda_fail(cudaError_t e, const char* what) {
+    g_last_error = std::string(what) + ": " + cudaGetErrorName(e) + " (" + cudaGetErrorString(e) + ")";
+    return B200_CUDA_ERROR;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+struct b200_handle {
+    int device = 0;
+    int sm_count = 0;
+    int* status_word = nullptr;  // 4 ints on the device
+    // options
+    int force_kernel = B200_KERNEL_AUTO;
+    int max_ctas = 0;
+    unsigned long long wait_budget_ns = 2000000000ull;
+    int tile_n = 0;
+    int split_k = 0;
+    int cta_pair = 0;
+    int relay_release = 0;
+    // workspace of the host-buffer entry point and split-K scratch (grown on demand)
+    void* ws[4] = {nullptr, nullptr, nullptr, nullptr};
+    size_t ws_bytes[4] = {0, 0, 0, 0};
+    float* scratch = nullptr;
+    size_t scratch_bytes = 0;
+    cudaStream_t own_stream = nullptr;
+    LaunchInfo last = {0, 0, 0, 0, 0};
+};
+
+namespace {
+
+int ensure_buffer(void** p, size_t* have, size_t need) {
+    if (need <= *have) return B200_OK;
+    if (*p) {
+        B200_CUDA_TRY(cudaFree(*p));
+        *p = nullptr;
+        *have = 0;
+    }
+    B200_CUDA_TRY(cudaMalloc(p, need));
+    *have = need;
+    return B200_OK;
+}
+
+int validate(const GemmProblem& g) {
+    if (g.M < 0 || g.N < 0 || g.K < 0) return fail(B200_INVALID_ARG, "gemm: negative dimension");
+    if ((g.transA != 0 && g.transA != 1) || (g.transB != 0 && g.transB != 1))
+        return fail(B200_INVALID_ARG, "gemm: transA / transB must be 0 or 1");
+    const int64_t a_rows = g.transA ? g.K : g.M, b_rows = g.transB ? g.N : g.K;
+    if (g.lda < std::max<int64_t>(1, a_rows)) return fail(B200_INVALID_ARG, "gemm: lda smaller than the rows of stored A");
+    if (g.ldb < std::max<int64_t>(1, b_rows)) return fail(B200_INVALID_ARG, "gemm: ldb smaller than the rows of stored B");
+    if (g.ldd < std::max<int64_t>(1, g.M)) return fail(B200_INVALID_ARG, "gemm: ldd smaller than M");
+    if (g.beta != 0.0f && g.ldc < std::max<int64_t>(1, g.M)) return fail(B200_INVALID_ARG, "gemm: ldc smaller than M");
+    if (g.M > 0 && g.N > 0) {
+        if (!g.D) return fail(B200_INVALID_ARG, "gemm: D is null");
+        if (g.beta != 0.0f && !g.C) return fail(B200_INVALID_ARG, "gemm: C is null but beta != 0");
+        if (g.K > 0 && (!g.A || !g.B)) return fail(B200_INVALID_ARG, "gemm: A or B is null");
+    }
+    return B200_OK;
+}
+
+// Tile shape and split heuristics.  Big square-ish problems take 2-CTA 256 x 256 tiles; narrow N
+// takes the narrowest tile that covers it, paired along M when there are rows enough.
+GemmPlan make_plan(const b200_handle* h, const GemmProblem& g) {
+    GemmPlan plan;
+    plan.max_ctas = h->max_ctas;
+    plan.relay_release = h->relay_release;
+    plan.wait_budget_ns = h->wait_budget_ns;
+    int tile_n = h->tile_n;
+    if (tile_n == 0) tile_n = g.N > 128 ? 256 : (g.N > 64 ? 128 : 64);
+    int pair = h->cta_pair;
+    if (pair == 0) pair = (g.M > 128 && tile_n >= 128) ? 2 : 1;
+    if (pair == 2 && tile_n < 128) pair = 1;
+    if (g.transB && (tile_n / pair) % 64) pair = 1;  // row-major B loads 64 columns per box
+    plan.tile_n = tile_n;
+    plan.cta_pair = pair;
+    plan.split_k = h->split_k > 0 ? h->split_k : 1;
+    return plan;
+}
+
+int run_gemm(b200_handle* h, cudaStream_t stream, const GemmProblem& g) {
+    int rc = validate(g);
+    if (rc) return rc;
+    if (g.M == 0 || g.N == 0) return B200_OK;
+    std::string why;
+    const bool eligible = gemm_tcgen05_eligible(g, &why);
+    int kernel = h->force_kernel;
+    if (kernel == B200_KERNEL_AUTO) kernel = eligible ? B200_KERNEL_TCGEN05 : B200_KERNEL_SIMPLE;
+    if (kernel == B200_KERNEL_TCGEN05) {
+        if (!eligible) return fail(B200_UNSUPPORTED, "tcgen05 kernel not eligible: " + why);
+        GemmPlan plan = make_plan(h, g);
+        const size_t need = gemm_tcgen05_scratch_bytes(g, plan);
+        if (need) {
+            void* p = h->scratch;
+            rc = ensure_buffer(&p, &h->scratch_bytes, need);
+            h->scratch = static_cast<float*>(p);
+            if (rc) return rc;
+        }
+        return gemm_tcgen05_launch(g, plan, h->scratch, h->status_word, h->sm_count, stream, &h->last);
+    }
+    if (kernel == B200_KERNEL_SIMPLE) return gemm_simple_launch(g, stream, &h->last);
+    return fail(B200_INVALID_ARG, "unknown kernel selector");
+}
+
+int read_status(b200_handle* h, int* word) {
+    B200_CUDA_TRY(cudaMemcpy(word, h->status_word, 4 * sizeof(int), cudaMemcpyDeviceToHost));
+    if (word[0] != 0) B200_CUDA_TRY(cudaMemset(h->status_word, 0, 4 * sizeof(int)));
+    return B200_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* b200_last_error(void) { return g_last_error.c_str(); }
+
+const char* b200_status_string(int status) {
+    switch (status) {
+        case B200_OK: return "B200_OK";
+        case B200_INVALID_ARG: return "B200_INVALID_ARG";
+        case B200_UNSUPPORTED: return "B200_UNSUPPORTED";
+        case B200_CUDA_ERROR: return "B200_CUDA_ERROR";
+        case B200_DEVICE_TIMEOUT: return "B200_DEVICE_TIMEOUT";
+        case B200_NO_DEVICE: return "B200_NO_DEVICE";
+        default: return "B200_UNKNOWN_STATUS";
+    }
+}
+
+int b200_version(void) { return 100; }
+
+int b200_device_count(void) {
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess) {
+        cuda_fail(e, "cudaGetDeviceCount");
+        return -B200_CUDA_ERROR;
+    }
+    int good = 0;
+    for (int d = 0; d < n; ++d) {
+        int major = 0;
+        if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, d) == cudaSuccess && major == 10) ++good;
+    }
+    return good;
+}
+
+int b200_create(b200_handle** out, int device) {
+    if (!out) return fail(B200_INVALID_ARG, "b200_create: out is null");
+    *out = nullptr;
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess || n == 0) {
+        cudaGetLastError();
+        return fail(B200_NO_DEVICE, std::string("b200_create: no CUDA device (") + cudaGetErrorString(e) + ")");
+    }
+    if (device < 0 || device >= n) return fail(B200_INVALID_ARG, "b200_create: device index out of range");
+    int major = 0, minor = 0, sms = 0;
+    B200_CUDA_TRY(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device));
+    B200_CUDA_TRY(cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, device));
+    B200_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+    if (major != 10)
+        return fail(B200_NO_DEVICE, "b200_create: device has compute capability " + std::to_string(major) + "." +
+                                        std::to_string(minor) + ", this library holds sm_100a code only");
+    B200_CUDA_TRY(cudaSetDevice(device));
+    b200_handle* h = new b200_handle();
+    h->device = device;
+    h->sm_count = sms;
+    if (cudaMalloc(&h->status_word, 4 * sizeof(int)) != cudaSuccess || cudaMemset(h->status_word, 0, 4 * sizeof(int)) != cudaSuccess) {
+        int rc = cuda_fail(cudaGetLastError(), "b200_create: status word");
+        delete h;
+        return rc;
+    }
+    *out = h;
+    return B200_OK;
+}
+
+int b200_destroy(b200_handle* h) {
+    if (!h) return B200_OK;
+    cudaSetDevice(h->device);
+    for (int i = 0; i < 4; ++i)
+        if (h->ws[i]) cudaFree(h->ws[i]);
+    if (h->scratch) cudaFree(h->scratch);
+    if (h->status_word) cudaFree(h->status_word);
+    if (h->own_stream) cudaStreamDestroy(h->own_stream);
+    delete h;
+    return B200_OK;
+}
+
+int b200_set_option(b200_handle* h, int option, int64_t value) {
+    if (!h) return fail(B200_INVALID_ARG, "null handle");
+    switch (option) {
+        case B200_OPT_FORCE_KERNEL:
+            if (value < B200_KERNEL_AUTO || value > B200_KERNEL_SIMPLE) return fail(B200_INVALID_ARG, "unknown kernel selector");
+            h->force_kernel = static_cast<int>(value);
+            return B200_OK;
+        case B200_OPT_MAX_CTAS:
+            if (value < 0) return fail(B200_INVALID_ARG, "max CTAs must be >= 0");
+            h->max_ctas = static_cast<int>(value);
+            return B200_OK;
+        case B200_OPT_WAIT_BUDGET_NS:
+            if (value < 1000) return fail(B200_INVALID_ARG, "wait budget below 1 us");
+            h->wait_budget_ns = static_cast<unsigned long long>(value);
+            return B200_OK;
+        case B200_OPT_TILE_N:
+            if (value != 0 && value != 64 && value != 128 && value != 256) return fail(B200_INVALID_ARG, "tile_n must be 0, 64, 128 or 256");
+            h->tile_n = static_cast<int>(value);
+            return B200_OK;
+        case B200_OPT_SPLIT_K:
+            if (value < 0 || value > 64) return fail(B200_INVALID_ARG, "split_k must be in [0, 64]");
+            h->split_k = static_cast<int>(value);
+            return B200_OK;
+        case B200_OPT_CTA_PAIR:
+            if (value < 0 || value > 2) return fail(B200_INVALID_ARG, "cta_pair must be 0, 1 or 2");
+            h->cta_pair = static_cast<int>(value);
+            return B200_OK;
+        case B200_OPT_RELAY_RELEASE:
+            h->relay_release = value ? 1 : 0;
+            return B200_OK;
+        default:
+            return fail(B200_INVALID_ARG, "unknown option");
+    }
+}
+
+int b200_get_option(b200_handle* h, int option, int64_t* value) {
+    if (!h || !value) return fail(B200_INVALID_ARG, "null handle or value");
+    switch (option) {
+        case B200_OPT_FORCE_KERNEL: *value = h->force_kernel; return B200_OK;
+        case B200_OPT_MAX_CTAS: *value = h->max_ctas; return B200_OK;
+        case B200_OPT_WAIT_BUDGET_NS: *value = static_cast<int64_t>(h->wait_budget_ns); return B200_OK;
+        case B200_OPT_TILE_N: *value = h->tile_n; return B200_OK;
+        case B200_OPT_SPLIT_K: *value = h->split_k; return B200_OK;
+        case B200_OPT_CTA_PAIR: *value = h->cta_pair; return B200_OK;
+        case B200_OPT_RELAY_RELEASE: *value = h->relay_release; return B200_OK;
+        default: return fail(B200_INVALID_ARG, "unknown option");
+    }
+}
+
+int b200_device_status(b200_handle* h, int* code, int* block, int* detail) {
+    if (!h) return fail(B200_INVALID_ARG, "null handle");
+    int word[4] = {0, 0, 0, 0};
+    int rc = read_status(h, word);
+    if (rc) return rc;
+    if (code) *code = word[0];
+    if (block) *block = word[1];
+    if (detail) *detail = word[2];
+    return B200_OK;
+}
+
+int b200_selftest_bounded_wait(b200_handle* h, b200_stream stream, int64_t budget_ns) {
+    if (!h) return fail(B200_INVALID_ARG, "null handle");
+    if (budget_ns < 1000 || budget_ns > 1000000000ll) return fail(B200_INVALID_ARG, "selftest budget must be within [1 us, 1 s]");
+    bounded_wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(h->status_word, static_cast<unsigned long long>(budget_ns));
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
+}
+
+int b200_last_launch(b200_handle* h, int* kernel, int* tile_n, int* split_k, int* ctas, int* cta_pair) {
+    if (!h) return fail(B200_INVALID_ARG, "null handle");
+    if (kernel) *kernel = h->last.kernel;
+    if (tile_n) *tile_n = h->last.tile_n;
+    if (split_k) *split_k = h->last.split_k;
+    if (ctas) *ctas = h->last.ctas;
+    if (cta_pair) *cta_pair = h->last.cta_pair;
+    return B200_OK;
+}
+
+int b200_gemm_f16f32(b200_handle* h, b200_stream stream, int transA, int transB, int64_t M, int64_t N, int64_t K,
+                     float alpha, const void* A, int64_t lda, const void* B, int64_t ldb, float beta, const float* C,
+                     int64_t ldc, float* D, int64_t ldd) {
+    if (!h) return fail(B200_INVALID_ARG, "null handle");
+    GemmProblem g{transA, transB, M, N, K, alpha, beta, A, lda, B, ldb, C, ldc, D, ldd};
+    return run_gemm(h, static_cast<cudaStream_t>(stream), g);
+}
+
+int b200_gemm_f16f32_host(b200_handle* h, int transA, int transB, int64_t M, int64_t N, int64_t K, float alpha,
+                          const void* A, int64_t lda, const void* B, int64_t ldb, float beta, const float* C,
+                          int64_t ldc, float* D, int64_t ldd) {
+    if (!h) return fail(B200_INVALID_ARG, "null handle");
+    GemmProblem hg{transA, transB, M, N, K, alpha, beta, A, lda, B, ldb, C, ldc, D, ldd};
+    int rc = validate(hg);
+    if (rc) return rc;
+    if (M == 0 || N == 0) return B200_OK;
+    B200_CUDA_TRY(cudaSetDevice(h->device));
+    if (!h->own_stream) B200_CUDA_TRY(cudaStreamCreateWithFlags(&h->own_stream, cudaStreamNonBlocking));
+    cudaStream_t s = h->own_stream;
+    const int64_t a_cols = transA ? M : K, b_cols = transB ? K : N;
+    const bool has_c = (beta != 0.0f);
+    const size_t a_bytes = static_cast<size_t>(lda) * a_cols * 2, b_bytes = static_cast<size_t>(ldb) * b_cols * 2;
+    const size_t c_bytes = has_c ? static_cast<size_t>(ldc) * N * 4 : 0, d_bytes = static_cast<size_t>(ldd) * N * 4;
+    if ((rc = ensure_buffer(&h->ws[0], &h->ws_bytes[0], std::max<size_t>(a_bytes, 16)))) return rc;
+    if ((rc = ensure_buffer(&h->ws[1], &h->ws_bytes[1], std::max<size_t>(b_bytes, 16)))) return rc;
+    if ((rc = ensure_buffer(&h->ws[2], &h->ws_bytes[2], std::max<size_t>(c_bytes, 16)))) return rc;
+    if ((rc = ensure_buffer(&h->ws[3], &h->ws_bytes[3], std::max<size_t>(d_bytes, 16)))) return rc;
+    if (K > 0) {
+        B200_CUDA_TRY(cudaMemcpyAsync(h->ws[0], A, a_bytes, cudaMemcpyHostToDevice, s));
+        B200_CUDA_TRY(cudaMemcpyAsync(h->ws[1], B, b_bytes, cudaMemcpyHostToDevice, s));
+    }
+    if (has_c) B200_CUDA_TRY(cudaMemcpyAsync(h->ws[2], C, c_bytes, cudaMemcpyHostToDevice, s));
+    GemmProblem g{transA, transB, M, N, K, alpha, beta, h->ws[0], lda, h->ws[1], ldb,
+                  static_cast<const float*>(h->ws[2]), ldc, static_cast<float*>(h->ws[3]), ldd};
+    if ((rc = run_gemm(h, s, g))) return rc;
+    if (ldd == M) {
+        B200_CUDA_TRY(cudaMemcpyAsync(D, h->ws[3], static_cast<size_t>(M) * N * 4, cudaMemcpyDeviceToHost, s));
+    } else {
+        // only the M x N window of D belongs to the operation
+        B200_CUDA_TRY(cudaMemcpy2DAsync(D, static_cast<size_t>(ldd) * 4, h->ws[3], static_cast<size_t>(ldd) * 4,
+                                        static_cast<size_t>(M) * 4, static_cast<size_t>(N), cudaMemcpyDeviceToHost, s));
+    }
+    B200_CUDA_TRY(cudaStreamSynchronize(s));
+    int word[4] = {0, 0, 0, 0};
+    if ((rc = read_status(h, word))) return rc;
+    if (word[0] != 0)
+        return fail(B200_DEVICE_TIMEOUT, "gemm: a bounded wait ran out on the device (wait id " + std::to_string(word[0]) +
+                                             ", block " + std::to_string(word[1]) + ")");
+    return B200_OK;
+}
+
+int b200_malloc(void** dptr, size_t bytes) {
+    if (!dptr) return fail(B200_INVALID_ARG, "b200_malloc: null out pointer");
+    *dptr = nullptr;
+    B200_CUDA_TRY(cudaMalloc(dptr, bytes ? bytes : 1));
+    return B200_OK;
+}
+int b200_free(void* dptr) {
+    if (dptr) B200_CUDA_TRY(cudaFree(dptr));
+    return B200_OK;
+}
+int b200_host_alloc(void** hptr, size_t bytes) {
+    if (!hptr) return fail(B200_INVALID_ARG, "b200_host_alloc: null out pointer");
+    *hptr = nullptr;
+    B200_CUDA_TRY(cudaHostAlloc(hptr, bytes ? bytes : 1, cudaHostAllocDefault));
+    return B200_OK;
+}
+int b200_host_free(void* hptr) {
+    if (hptr) B200_CUDA_TRY(cudaFreeHost(hptr));
+    return B200_OK;
+}
+int b200_memcpy_h2d(void* dst, const void* src, size_t bytes, b200_stream stream) {
+    B200_CUDA_TRY(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream)));
+    return B200_OK;
+}
+int b200_memcpy_d2h(void* dst, const void* src, size_t bytes, b200_stream stream) {
+    B200_CUDA_TRY(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)));
+    return B200_OK;
+}
+int b200_memset(void* dst, int byte, size_t bytes, b200_stream stream) {
+    B200_CUDA_TRY(cudaMemsetAsync(dst, byte, bytes, static_cast<cudaStream_t>(stream)));
+    return B200_OK;
+}
+int b200_stream_sync(b200_stream stream) {
+    B200_CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+    return B200_OK;
+}
+
+}  // extern "C"

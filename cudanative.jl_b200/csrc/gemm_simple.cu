@@ -1,0 +1,142 @@
+// Plain shared-memory GEMM (FP32 FMA on CUDA cores) and the synthetic-matrix fill kernels.
+//
+// The simple kernel takes any shape, leading dimension and alignment, so it backs the shapes the
+// TMA path cannot address (unaligned pointers, K == 0) and serves as an independent on-device
+// check of the tcgen05 kernel at sizes a CPU product would take minutes for.  Products of two
+// binary16 values are exact in binary32, so it differs from the tensor-core result only in the
+// order of the FP32 additions.
+#include <cuda_fp16.h>
+
+#include "internal.h"
+#include "rng.cuh"
+
+namespace b200 {
+namespace {
+
+constexpr int kTile = 64;   // output tile per block
+constexpr int kTileK = 16;  // k per shared-memory step
+
+template <bool kTransA, bool kTransB>
+__global__ void __launch_bounds__(256)
+gemm_simple_kernel(int64_t M, int64_t N, int64_t K, float alpha, const __half* __restrict__ A, int64_t lda,
+                   const __half* __restrict__ B, int64_t ldb, float beta, const float* C, int64_t ldc, float* D,
+                   int64_t ldd) {
+    __shared__ float sA[kTileK][kTile + 1];
+    __shared__ float sB[kTileK][kTile + 1];
+    const int tx = threadIdx.x & 15;  // 4 rows each
+    const int ty = threadIdx.x >> 4;  // 4 cols each
+    const int64_t m0 = static_cast<int64_t>(blockIdx.x) * kTile;
+    const int64_t n0 = static_cast<int64_t>(blockIdx.y) * kTile;
+    float acc[4][4] = {};
+    for (int64_t k0 = 0; k0 < K; k0 += kTileK) {
+        for (int e = threadIdx.x; e < kTile * kTileK; e += 256) {
+            int mm, kk;
+            if (kTransA) { kk = e % kTileK; mm = e / kTileK; } else { mm = e % kTile; kk = e / kTile; }
+            const int64_t m = m0 + mm, k = k0 + kk;
+            float v = 0.f;
+            if (m < M && k < K) v = __half2float(kTransA ? A[k + m * lda] : A[m + k * lda]);
+            sA[kk][mm] = v;
+        }
+        for (int e = threadIdx.x; e < kTile * kTileK; e += 256) {
+            int nn, kk;
+            if (kTransB) { nn = e % kTile; kk = e / kTile; } else { kk = e % kTileK; nn = e / kTileK; }
+            const int64_t n = n0 + nn, k = k0 + kk;
+            float v = 0.f;
+            if (n < N && k < K) v = __half2float(kTransB ? B[n + k * ldb] : B[k + n * ldb]);
+            sB[kk][nn] = v;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < kTileK; ++kk) {
+            float a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = sA[kk][tx * 4 + i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) b[j] = sB[kk][ty * 4 + j];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int64_t n = n0 + ty * 4 + j;
+        if (n >= N) continue;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int64_t m = m0 + tx * 4 + i;
+            if (m >= M) continue;
+            float v = alpha * acc[i][j];
+            if (beta != 0.0f) v = fmaf(beta, C[m + n * ldc], v);
+            D[m + n * ldd] = v;
+        }
+    }
+}
+
+template <typename T>
+__global__ void fill_kernel(T* out, int64_t rows, int64_t cols, int64_t ld, uint64_t seed, uint64_t matrix_id,
+                            uint64_t index0, int dist, float scale) {
+    const int64_t total = rows * cols;
+    for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < total;
+         idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t j = idx / rows, i = idx - j * rows;
+        const float v = synth_value(seed, matrix_id, index0 + static_cast<uint64_t>(idx), dist) * scale;
+        if constexpr (sizeof(T) == 2) out[i + j * ld] = __float2half_rn(v);
+        else out[i + j * ld] = v;
+    }
+}
+
+template <typename T>
+int fill_launch(cudaStream_t stream, T* dptr, int64_t rows, int64_t cols, int64_t ld, uint64_t seed,
+                uint64_t matrix_id, uint64_t index0, int dist, float scale) {
+    if (rows < 0 || cols < 0 || ld < rows || (rows * cols > 0 && !dptr)) return fail(B200_INVALID_ARG, "fill: bad matrix");
+    if (dist < 0 || dist > 2) return fail(B200_INVALID_ARG, "fill: dist must be 0 (uniform), 1 (normal) or 2 (zeros)");
+    const int64_t total = rows * cols;
+    if (total == 0) return B200_OK;
+    int64_t blocks = (total + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    fill_kernel<T><<<static_cast<int>(blocks), 256, 0, stream>>>(dptr, rows, cols, ld, seed, matrix_id, index0, dist, scale);
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
+}
+
+}  // namespace
+
+int gemm_simple_launch(const GemmProblem& g, cudaStream_t stream, LaunchInfo* info) {
+    if (g.M == 0 || g.N == 0) return B200_OK;
+    const int64_t gx = (g.M + kTile - 1) / kTile, gy = (g.N + kTile - 1) / kTile;
+    if (gy > 65535) return fail(B200_UNSUPPORTED, "simple kernel: N too large for one launch");
+    dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(gy));
+    const __half* A = static_cast<const __half*>(g.A);
+    const __half* B = static_cast<const __half*>(g.B);
+#define B200_SIMPLE(TA, TB) \
+    gemm_simple_kernel<TA, TB><<<grid, 256, 0, stream>>>(g.M, g.N, g.K, g.alpha, A, g.lda, B, g.ldb, g.beta, g.C, g.ldc, g.D, g.ldd)
+    if (g.transA) { if (g.transB) B200_SIMPLE(true, true); else B200_SIMPLE(true, false); }
+    else          { if (g.transB) B200_SIMPLE(false, true); else B200_SIMPLE(false, false); }
+#undef B200_SIMPLE
+    B200_CUDA_TRY(cudaGetLastError());
+    if (info) {
+        info->kernel = B200_KERNEL_SIMPLE;
+        info->tile_n = kTile;
+        info->split_k = 1;
+        info->ctas = static_cast<int>(gx * gy);
+        info->cta_pair = 1;
+    }
+    return B200_OK;
+}
+
+}  // namespace b200
+
+extern "C" int b200_fill_f16(b200_stream stream, void* dptr, int64_t rows, int64_t cols, int64_t ld, uint64_t seed,
+                             uint64_t matrix_id, uint64_t index0, int dist, float scale) {
+    return b200::fill_launch<__half>(static_cast<cudaStream_t>(stream), static_cast<__half*>(dptr), rows, cols, ld,
+                                     seed, matrix_id, index0, dist, scale);
+}
+
+extern "C" int b200_fill_f32(b200_stream stream, float* dptr, int64_t rows, int64_t cols, int64_t ld, uint64_t seed,
+                             uint64_t matrix_id, uint64_t index0, int dist, float scale) {
+    return b200::fill_launch<float>(static_cast<cudaStream_t>(stream), dptr, rows, cols, ld, seed, matrix_id, index0,
+                                    dist, scale);
+}

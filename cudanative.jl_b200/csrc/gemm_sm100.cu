@@ -1,0 +1,241 @@
+// Host side of the tcgen05 GEMM: tensor-map construction, kernel selection, launch.
+#include "gemm_sm100.cuh"
+
+#include <cudaTypedefs.h>
+
+#include <mutex>
+
+#include "internal.h"
+
+namespace b200 {
+namespace {
+
+using EncodeFn = PFN_cuTensorMapEncodeTiled_v12000;
+
+// cuTensorMapEncodeTiled through the runtime's driver entry-point lookup: no link-time
+// dependency on libcuda.
+EncodeFn get_encode_fn() {
+    static EncodeFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeFn>(p);
+    });
+    return fn;
+}
+
+// 2-D tensor map over a column-major matrix: dim0 (contiguous) has `inner` elements, dim1 has
+// `outer` elements `ld` elements apart.
+int make_map_2d(CUtensorMap* tm, CUtensorMapDataType dt, int elem_bytes, const void* base, int64_t inner,
+                int64_t outer, int64_t ld, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle sw,
+                const char* what) {
+    EncodeFn enc = get_encode_fn();
+    if (!enc) return fail(B200_CUDA_ERROR, "cuTensorMapEncodeTiled entry point not found");
+    cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * elem_bytes};
+    cuuint32_t box[2] = {box_inner, box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(tm, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(B200_CUDA_ERROR, std::string("cuTensorMapEncodeTiled failed for ") + what + " (CUresult " +
+                                         std::to_string(static_cast<int>(r)) + ")");
+    return B200_OK;
+}
+
+template <int kBN, bool kAMn, bool kBMn, int kCtas>
+int launch_one(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const CUtensorMap& tmD,
+               const GemmParams& p, int grid, cudaStream_t stream) {
+    using Cfg = GemmCfg<kBN, kAMn, kBMn, kCtas>;
+    auto kern = gemm_f16f32_tcgen05<kBN, kAMn, kBMn, kCtas>;
+    // per device and per function; cheap enough to repeat on every launch
+    B200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(Cfg::THREADS, 1, 1);
+    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = kCtas;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    B200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmC, tmD, p));
+    return B200_OK;
+}
+
+template <int kBN, int kCtas>
+int launch_layout(bool a_mn, bool b_mn, const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
+                  const CUtensorMap& tmD, const GemmParams& p, int grid, cudaStream_t stream) {
+    if (a_mn) {
+        if (b_mn) return launch_one<kBN, true, true, kCtas>(tmA, tmB, tmC, tmD, p, grid, stream);
+        return launch_one<kBN, true, false, kCtas>(tmA, tmB, tmC, tmD, p, grid, stream);
+    }
+    if (b_mn) return launch_one<kBN, false, true, kCtas>(tmA, tmB, tmC, tmD, p, grid, stream);
+    return launch_one<kBN, false, false, kCtas>(tmA, tmB, tmC, tmD, p, grid, stream);
+}
+
+inline int64_t round_up(int64_t x, int64_t m) { return (x + m - 1) / m * m; }
+
+struct Geometry {
+    int tiles_m, tiles_n, kb_total, split_k, kb_per_split;
+    int64_t ws_ld;        // leading dimension of the split-K scratch matrix
+    int ws_n_stride;      // columns per k-slice in the scratch matrix
+};
+
+Geometry geometry(const GemmProblem& g, const GemmPlan& plan) {
+    Geometry q;
+    const int tile_m = 128 * plan.cta_pair;
+    q.tiles_m = static_cast<int>((g.M + tile_m - 1) / tile_m);
+    q.tiles_n = static_cast<int>((g.N + plan.tile_n - 1) / plan.tile_n);
+    q.kb_total = static_cast<int>((g.K + 63) / 64);
+    int s = plan.split_k < 1 ? 1 : plan.split_k;
+    if (s > q.kb_total) s = q.kb_total;
+    q.kb_per_split = (q.kb_total + s - 1) / s;
+    q.split_k = (q.kb_total + q.kb_per_split - 1) / q.kb_per_split;  // no empty slices
+    q.ws_ld = round_up(g.M, 4);
+    q.ws_n_stride = q.tiles_n * plan.tile_n;
+    return q;
+}
+
+}  // namespace
+
+size_t gemm_tcgen05_scratch_bytes(const GemmProblem& g, const GemmPlan& plan) {
+    const Geometry q = geometry(g, plan);
+    if (q.split_k <= 1) return 0;
+    return static_cast<size_t>(q.ws_ld) * q.ws_n_stride * q.split_k * sizeof(float);
+}
+
+bool gemm_tcgen05_eligible(const GemmProblem& g, std::string* why) {
+    auto no = [&](const char* m) {
+        if (why) *why = m;
+        return false;
+    };
+    if (g.M <= 0 || g.N <= 0 || g.K <= 0) return no("empty problem");
+    if (g.M > 0x7fffff00ll || g.N > 0x7fffff00ll || g.K > 0x7fffff00ll) return no("dimension exceeds 2^31");
+    if ((reinterpret_cast<uintptr_t>(g.A) | reinterpret_cast<uintptr_t>(g.B) | reinterpret_cast<uintptr_t>(g.D)) & 15u)
+        return no("A, B and D must be 16-byte aligned for TMA");
+    if (g.beta != 0.0f && (reinterpret_cast<uintptr_t>(g.C) & 15u)) return no("C must be 16-byte aligned for TMA");
+    if ((g.lda % 8) || (g.ldb % 8)) return no("lda and ldb must be multiples of 8 elements for TMA");
+    if ((g.ldd % 4) || (g.beta != 0.0f && (g.ldc % 4))) return no("ldc and ldd must be multiples of 4 elements for TMA");
+    return true;
+}
+
+int gemm_tcgen05_launch(const GemmProblem& g, const GemmPlan& plan, float* scratch, int* status_word, int sm_count,
+                        cudaStream_t stream, LaunchInfo* info) {
+    const Geometry q = geometry(g, plan);
+    const bool a_mn = (g.transA == 0);  // column-major M x K: M contiguous
+    const bool b_mn = (g.transB != 0);  // stored N x K column-major: N contiguous
+    const int bn_local = plan.tile_n / plan.cta_pair;
+    if (b_mn && (bn_local % 64)) return fail(B200_UNSUPPORTED, "row-major B needs at least 64 tile columns per CTA");
+    if (q.split_k > 1 && !scratch) return fail(B200_INVALID_ARG, "split-K launch without scratch");
+
+    CUtensorMap tmA, tmB, tmC, tmD;
+    int rc;
+    if (a_mn)
+        rc = make_map_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.A, g.M, g.K, g.lda, 64, 64,
+                         CU_TENSOR_MAP_SWIZZLE_128B, "A (column-major)");
+    else
+        rc = make_map_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.A, g.K, g.M, g.lda, 64, 128,
+                         CU_TENSOR_MAP_SWIZZLE_128B, "A (row-major)");
+    if (rc) return rc;
+    if (b_mn)
+        rc = make_map_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.B, g.N, g.K, g.ldb, 64, 64,
+                         CU_TENSOR_MAP_SWIZZLE_128B, "B (row-major)");
+    else
+        rc = make_map_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.B, g.K, g.N, g.ldb, 64, bn_local,
+                         CU_TENSOR_MAP_SWIZZLE_128B, "B (column-major)");
+    if (rc) return rc;
+
+    GemmParams p = {};
+    p.M = static_cast<int>(g.M);
+    p.N = static_cast<int>(g.N);
+    p.K = static_cast<int>(g.K);
+    p.tiles_m = q.tiles_m;
+    p.tiles_n = q.tiles_n;
+    p.split_k = q.split_k;
+    p.kb_total = q.kb_total;
+    p.kb_per_split = q.kb_per_split;
+    p.raster_group = 8;
+    p.relay_release = plan.relay_release;
+    p.status = status_word;
+    p.wait_budget_ns = plan.wait_budget_ns;
+
+    if (q.split_k > 1) {
+        // partial products go to scratch (k-slice s occupies columns [s * stride, s * stride + N))
+        rc = make_map_2d(&tmD, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, scratch, g.M, static_cast<int64_t>(q.ws_n_stride) * q.split_k,
+                         q.ws_ld, 128, 32, CU_TENSOR_MAP_SWIZZLE_NONE, "split-K scratch");
+        if (rc) return rc;
+        tmC = tmD;
+        p.alpha = 1.0f;
+        p.beta = 0.0f;
+        p.out_n_stride = q.ws_n_stride;
+    } else {
+        rc = make_map_2d(&tmD, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, g.D, g.M, g.N, g.ldd, 128, 32,
+                         CU_TENSOR_MAP_SWIZZLE_NONE, "D");
+        if (rc) return rc;
+        if (g.beta != 0.0f) {
+            rc = make_map_2d(&tmC, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, g.C, g.M, g.N, g.ldc, 128, 32,
+                             CU_TENSOR_MAP_SWIZZLE_NONE, "C");
+            if (rc) return rc;
+        } else {
+            tmC = tmD;  // never dereferenced
+        }
+        p.alpha = g.alpha;
+        p.beta = g.beta;
+        p.out_n_stride = 0;
+    }
+
+    const int units = q.tiles_m * q.tiles_n * q.split_k;
+    int cap = plan.max_ctas > 0 ? plan.max_ctas : sm_count;
+    if (cap > sm_count) cap = sm_count;
+    int grid;
+    if (plan.cta_pair == 2) {
+        int clusters = cap / 2;
+        if (clusters < 1) clusters = 1;
+        if (clusters > units) clusters = units;
+        grid = clusters * 2;
+    } else {
+        grid = cap < units ? cap : units;
+        if (grid < 1) grid = 1;
+    }
+
+    if (plan.cta_pair == 2) {
+        if (plan.tile_n == 256) rc = launch_layout<256, 2>(a_mn, b_mn, tmA, tmB, tmC, tmD, p, grid, stream);
+        else if (plan.tile_n == 128) rc = launch_layout<128, 2>(a_mn, b_mn, tmA, tmB, tmC, tmD, p, grid, stream);
+        else return fail(B200_UNSUPPORTED, "2-CTA tiles exist for tile_n 128 and 256");
+    } else {
+        if (plan.tile_n == 256) rc = launch_layout<256, 1>(a_mn, b_mn, tmA, tmB, tmC, tmD, p, grid, stream);
+        else if (plan.tile_n == 128) rc = launch_layout<128, 1>(a_mn, b_mn, tmA, tmB, tmC, tmD, p, grid, stream);
+        else if (plan.tile_n == 64) rc = launch_layout<64, 1>(a_mn, b_mn, tmA, tmB, tmC, tmD, p, grid, stream);
+        else return fail(B200_UNSUPPORTED, "tile_n must be 64, 128 or 256");
+    }
+    if (rc) return rc;
+
+    if (q.split_k > 1) {
+        const bool vec_ok = !((reinterpret_cast<uintptr_t>(g.D) & 15u) || (g.ldd % 4) ||
+                              (g.beta != 0.0f && ((reinterpret_cast<uintptr_t>(g.C) & 15u) || (g.ldc % 4))));
+        const long long quads = (g.M + 3) / 4 * g.N;
+        int blocks = static_cast<int>((quads + 255) / 256);
+        if (blocks > sm_count * 8) blocks = sm_count * 8;
+        if (blocks < 1) blocks = 1;
+        gemm_splitk_reduce<<<blocks, 256, 0, stream>>>(scratch, q.ws_ld, q.ws_n_stride, q.split_k, p.M, p.N, g.alpha,
+                                                       g.beta, g.C, g.ldc, g.D, g.ldd, vec_ok ? 1 : 0);
+        B200_CUDA_TRY(cudaGetLastError());
+    }
+    if (info) {
+        info->kernel = B200_KERNEL_TCGEN05;
+        info->tile_n = plan.tile_n;
+        info->split_k = q.split_k;
+        info->ctas = grid;
+        info->cta_pair = plan.cta_pair;
+    }
+    return B200_OK;
+}
+
+}  // namespace b200

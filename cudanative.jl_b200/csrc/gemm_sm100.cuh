@@ -1,0 +1,407 @@
+// Persistent, warp-specialised FP16 x FP16 -> FP32 GEMM for sm_100a.
+//
+//   D = alpha * op(A) * op(B) + beta * C        (column-major C / D, FP32 epilogue)
+//
+// This is the many-tile form of the reference's load_a / load_b / load_c -> mma -> store_d
+// sequence (src/device/cuda/wmma.jl:507-632 of CUDAnative.jl): "fragments" are shared-memory
+// tiles filled by TMA, the multiply-accumulate is tcgen05.mma with the accumulator in tensor
+// memory, and the alpha/beta broadcast of wmma.jl:678-716 is fused into the epilogue.
+//
+// One CTA (or a pair of CTAs on neighbouring SMs, kCtas == 2) owns an output tile of
+// (128 * kCtas) x kBN.  Roles, by warp:
+//   warp 0    TMA producer: streams 128 x 64 slices of op(A) and (kBN / kCtas) x 64 slices of
+//             op(B) into a ring of shared-memory stages (128-byte swizzle)
+//   warp 1    MMA issuer: one thread issues tcgen05.mma (K = 16 per instruction, 4 per stage)
+//             and commits stage-release / accumulator-ready barriers
+//   warp 2    allocates and frees tensor memory (two accumulators of kBN columns)
+//   warp 3    idle
+//   warps 4-7 epilogue: tcgen05.ld the accumulator (lane = row), combine with C staged in
+//             shared memory by TMA, write the result back into the same staging buffer and
+//             TMA-store it; double-buffered in chunks of 32 columns
+// The two accumulators let the epilogue of tile i overlap the main loop of tile i + 1.
+//
+// Work units are (tile, k-slice) pairs; with split_k > 1 each unit writes a raw FP32 partial
+// product to a scratch matrix and a second kernel reduces them (gemm_splitk_reduce).
+//
+// Every barrier wait is bounded (ptx_sm100.cuh: mbar_wait); on expiry the CTA records the wait
+// in the device status word and every role falls through to the common exit.
+#pragma once
+
+#include "ptx_sm100.cuh"
+
+namespace b200 {
+
+struct GemmParams {
+    int M, N, K;
+    int tiles_m, tiles_n;  // tile grid; a tile is (128 * kCtas) x kBN
+    int split_k;           // k-slices per tile (>= 1)
+    int kb_total;          // ceil(K / 64)
+    int kb_per_split;      // ceil(kb_total / split_k)
+    int raster_group;      // tiles_m per rasterisation group
+    int out_n_stride;      // column offset between k-slices in the output map (split_k > 1)
+    int relay_release;     // pair kernels: 1 = release peer stages by a relayed arrive
+    float alpha, beta;     // epilogue scalars (split_k > 1: 1 and 0)
+    int* status;
+    unsigned long long wait_budget_ns;
+};
+
+template <int kBN, bool kAMn, bool kBMn, int kCtas>
+struct GemmCfg {
+    static constexpr int BM = 128;                 // rows per CTA
+    static constexpr int BK = 64;                  // k per stage: one 128-byte swizzle row
+    static constexpr int BN = kBN;                 // columns per tile
+    static constexpr int BN_LOCAL = kBN / kCtas;   // B rows this CTA loads
+    static constexpr int A_BYTES = BM * BK * 2;
+    static constexpr int B_BYTES = BN_LOCAL * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int EPI_COLS = 32;
+    static constexpr int EPI_BYTES = BM * EPI_COLS * 4;
+    static constexpr int EPI_BUFS = 2;
+    static constexpr int SMEM_BUDGET = 227 * 1024 - 1024 /*alignment slack*/ - 512 /*barriers*/;
+    static constexpr int STAGES_RAW = (SMEM_BUDGET - EPI_BUFS * EPI_BYTES) / STAGE_BYTES;
+    static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+    static constexpr int TMEM_COLS = 2 * kBN < 32 ? 32 : 2 * kBN;
+    static constexpr int NCHUNK = kBN / EPI_COLS;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BUFS * EPI_BYTES + 512 + 1024;
+    static constexpr int THREADS = 256;
+    static_assert(kBN % 32 == 0 && kBN >= 32 && kBN <= 256, "tile N");
+    static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0 && TMEM_COLS <= 512, "TMEM columns");
+    static_assert(STAGES >= 2, "pipeline depth");
+    static_assert(kCtas == 1 || kCtas == 2, "CTAs per tile");
+    static_assert(!kBMn || (BN_LOCAL % 64 == 0), "MN-major B loads 64 columns per box");
+    static_assert(SMEM_BYTES <= 227 * 1024, "shared memory");
+};
+
+// Maps a linear tile index to (tile_m, tile_n): tiles walk down M inside groups of
+// `raster_group` tile rows so that concurrently running CTAs share A and B panels in L2.
+__device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& tm, int& tn) {
+    const int per_group = p.raster_group * p.tiles_n;
+    const int group = tile / per_group;
+    const int first_m = group * p.raster_group;
+    const int rows = min(p.raster_group, p.tiles_m - first_m);
+    const int idx = tile - group * per_group;
+    tm = first_m + idx % rows;
+    tn = idx / rows;
+}
+
+template <int kBN, bool kAMn, bool kBMn, int kCtas>
+__global__ void __launch_bounds__(256, 1)
+gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmD,
+                    const GemmParams p) {
+    using Cfg = GemmCfg<kBN, kAMn, kBMn, kCtas>;
+    constexpr int STAGES = Cfg::STAGES;
+    constexpr bool kPair = (kCtas == 2);
+
+    extern __shared__ uint8_t smem_raw[];
+    // 128-byte swizzling is a function of the shared-memory address: stages start on 1 KiB.
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+
+    const uint32_t stages_base = smem_base;
+    const uint32_t epi_base = smem_base + STAGES * Cfg::STAGE_BYTES;
+    const uint32_t bar_base = epi_base + Cfg::EPI_BUFS * Cfg::EPI_BYTES;
+    float* epi_gen = reinterpret_cast<float*>(smem_gen + STAGES * Cfg::STAGE_BYTES);
+    uint8_t* bar_gen = smem_gen + STAGES * Cfg::STAGE_BYTES + Cfg::EPI_BUFS * Cfg::EPI_BYTES;
+
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+    auto tmem_full_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+    auto tmem_empty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+    auto cfull_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + 4 + b); };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_gen + 8 * (2 * STAGES + 6));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_gen + 8 * (2 * STAGES + 6) + 4);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t cta_rank = kPair ? cluster_cta_rank() : 0u;
+    const int unit_stride = kPair ? (gridDim.x >> 1) : gridDim.x;
+    const int unit_first = kPair ? (blockIdx.x >> 1) : blockIdx.x;
+    const int num_units = p.tiles_m * p.tiles_n * p.split_k;
+
+    WaitCtx wc{abort_flag, p.status, p.wait_budget_ns};
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar(s), kCtas);   // one arrive(+tx) per CTA of the tile
+            mbar_init(empty_bar(s), 1);      // one tcgen05.commit (or one relayed arrive)
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(tmem_full_bar(a), 1);
+            mbar_init(tmem_empty_bar(a), 128 * kCtas);
+        }
+        for (int b = 0; b < Cfg::EPI_BUFS; ++b) mbar_init(cfull_bar(b), 1);
+        fence_mbar_init();
+        tma_prefetch_desc(&tmA);
+        tma_prefetch_desc(&tmB);
+        tma_prefetch_desc(&tmC);
+        tma_prefetch_desc(&tmD);
+    }
+    if (warp == 2) tmem_alloc<kCtas>(smem_u32(const_cast<uint32_t*>(tmem_slot)), Cfg::TMEM_COLS);
+    tc_fence_before_sync();
+    __syncthreads();
+    if constexpr (kPair) cluster_sync_all();  // peer barriers exist before anyone signals them
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    // unit -> (tile row, tile col, k-block range)
+    auto unit_decode = [&](int unit, int& m0, int& n0, int& kb0, int& kb1, int& out_n0) {
+        const int tile = unit / p.split_k;
+        const int slice = unit - tile * p.split_k;
+        int tm, tn;
+        tile_coords(p, tile, tm, tn);
+        m0 = tm * (Cfg::BM * kCtas) + static_cast<int>(cta_rank) * Cfg::BM;
+        n0 = tn * kBN;
+        kb0 = slice * p.kb_per_split;
+        kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+        out_n0 = n0 + slice * p.out_n_stride;
+    };
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int unit = unit_first; ok && unit < num_units; unit += unit_stride) {
+                int m0, n0, kb0, kb1, out_n0;
+                unit_decode(unit, m0, n0, kb0, kb1, out_n0);
+                const int nb0 = n0 + static_cast<int>(cta_rank) * Cfg::BN_LOCAL;
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1u;
+                    ok = mbar_wait<kPair>(empty_bar(s), ph ^ 1u, wc, kWaitEmptyStage);
+                    if (!ok) break;
+                    if (kPair && p.relay_release && cta_rank == 0 && it >= STAGES) {
+                        // the leader's stage is free, hence the MMAs that read the peer's
+                        // copy of the stage are complete as well: pass the release on
+                        mbar_arrive_cluster(empty_bar(s), 1);
+                    }
+                    const uint32_t sa = stages_base + s * Cfg::STAGE_BYTES;
+                    const uint32_t sb = sa + Cfg::A_BYTES;
+                    const int k0 = kb * Cfg::BK;
+                    if constexpr (!kPair) {
+                        const uint32_t fb = full_bar(s);
+                        mbar_arrive_expect_tx(fb, Cfg::STAGE_BYTES);
+                        if constexpr (kAMn) {
+                            tma_load_2d(sa, &tmA, m0, k0, fb);
+                            tma_load_2d(sa + 8192, &tmA, m0 + 64, k0, fb);
+                        } else {
+                            tma_load_2d(sa, &tmA, k0, m0, fb);
+                        }
+                        if constexpr (kBMn) {
+#pragma unroll
+                            for (int i = 0; i < Cfg::BN_LOCAL / 64; ++i)
+                                tma_load_2d(sb + i * 8192, &tmB, nb0 + i * 64, k0, fb);
+                        } else {
+                            tma_load_2d(sb, &tmB, k0, nb0, fb);
+                        }
+                    } else {
+                        // both CTAs of the pair report their bytes to the leader's barrier
+                        const uint32_t fb = mapa_shared(full_bar(s), 0);
+                        mbar_arrive_expect_tx_cluster(fb, Cfg::STAGE_BYTES);
+                        if constexpr (kAMn) {
+                            tma_load_2d_pair(sa, &tmA, m0, k0, fb);
+                            tma_load_2d_pair(sa + 8192, &tmA, m0 + 64, k0, fb);
+                        } else {
+                            tma_load_2d_pair(sa, &tmA, k0, m0, fb);
+                        }
+                        if constexpr (kBMn) {
+#pragma unroll
+                            for (int i = 0; i < Cfg::BN_LOCAL / 64; ++i)
+                                tma_load_2d_pair(sb + i * 8192, &tmB, nb0 + i * 64, k0, fb);
+                        } else {
+                            tma_load_2d_pair(sb, &tmB, k0, nb0, fb);
+                        }
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0 && cta_rank == 0) {
+            constexpr uint32_t idesc =
+                make_idesc_f16_f32(Cfg::BM * kCtas, kBN, kAMn ? 1 : 0, kBMn ? 1 : 0);
+            uint32_t it = 0, ucount = 0;
+            bool ok = true;
+            for (int unit = unit_first; ok && unit < num_units; unit += unit_stride, ++ucount) {
+                int m0, n0, kb0, kb1, out_n0;
+                unit_decode(unit, m0, n0, kb0, kb1, out_n0);
+                const uint32_t acc = ucount & 1u;
+                const uint32_t aph = (ucount >> 1) & 1u;
+                ok = mbar_wait<kPair>(tmem_empty_bar(acc), aph ^ 1u, wc, kWaitTmemEmpty);
+                if (!ok) break;
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + acc * kBN;
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1u;
+                    ok = mbar_wait<kPair>(full_bar(s), ph, wc, kWaitFullStage);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    const uint32_t sa = stages_base + s * Cfg::STAGE_BYTES;
+                    const uint32_t sb = sa + Cfg::A_BYTES;
+#pragma unroll
+                    for (int k = 0; k < Cfg::BK / 16; ++k) {
+                        // K-major tile: rows of 128 B, 8-row groups 1 KiB apart, k advances
+                        // 32 B inside the swizzled row.  MN-major tile: 64 (m or n) x 64 k
+                        // boxes of 8 KiB, 8-k groups 1 KiB apart, k = 16 advances 2 KiB.
+                        const uint64_t da = kAMn ? make_smem_desc(sa + k * 2048, 8192, 1024, kSwizzle128B)
+                                                 : make_smem_desc(sa + k * 32, 16, 1024, kSwizzle128B);
+                        const uint64_t db = kBMn ? make_smem_desc(sb + k * 2048, 8192, 1024, kSwizzle128B)
+                                                 : make_smem_desc(sb + k * 32, 16, 1024, kSwizzle128B);
+                        umma_f16<kCtas>(d_tmem, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit<kCtas>(empty_bar(s));
+                    if (kPair && !p.relay_release) umma_commit<kCtas>(mapa_shared(empty_bar(s), 1));
+                }
+                if (!ok) break;
+                umma_commit<kCtas>(tmem_full_bar(acc));
+                if constexpr (kPair) umma_commit<kCtas>(mapa_shared(tmem_full_bar(acc), 1));
+            }
+        }
+        __syncwarp();
+    } else if (warp >= 4) {
+        // ------------------------------------------------------------------ epilogue
+        const int et = threadIdx.x - 128;          // 0..127 = accumulator row inside the CTA
+        const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        const bool elected = (et == 0);
+        const bool has_c = (p.beta != 0.0f);
+        const float alpha = p.alpha, beta = p.beta;
+
+        auto chunks_of = [&](int n0) { return min(Cfg::NCHUNK, (p.N - n0 + Cfg::EPI_COLS - 1) / Cfg::EPI_COLS); };
+
+        uint32_t g = 0;  // chunk counter: staging buffer g & 1, C-barrier phase (g >> 1) & 1
+        if (has_c && elected && unit_first < num_units) {
+            int m0, n0, kb0, kb1, out_n0;
+            unit_decode(unit_first, m0, n0, kb0, kb1, out_n0);
+            mbar_arrive_expect_tx(cfull_bar(0), Cfg::EPI_BYTES);
+            tma_load_2d(epi_base, &tmC, m0, n0, cfull_bar(0));
+        }
+        uint32_t ucount = 0;
+        bool fail = false;
+        for (int unit = unit_first; unit < num_units; unit += unit_stride, ++ucount) {
+            int m0, n0, kb0, kb1, out_n0;
+            unit_decode(unit, m0, n0, kb0, kb1, out_n0);
+            const int nchunks = chunks_of(n0);
+            const uint32_t acc = ucount & 1u;
+            const uint32_t aph = (ucount >> 1) & 1u;
+            bool ok = mbar_wait<kPair>(tmem_full_bar(acc), aph, wc, kWaitTmemFull);
+            tc_fence_after_sync();
+            for (int j = 0; j < nchunks; ++j, ++g) {
+                const uint32_t buf = g & 1u;
+                if (elected) {
+                    if (has_c) {
+                        // fetch the next chunk of C into the other buffer once the store that
+                        // last used it has finished reading shared memory
+                        int nm0 = m0, nn0 = n0 + (j + 1) * Cfg::EPI_COLS;
+                        bool have_next = (j + 1 < nchunks);
+                        if (!have_next && unit + unit_stride < num_units) {
+                            int a, b, c;
+                            unit_decode(unit + unit_stride, nm0, nn0, a, b, c);
+                            have_next = true;
+                        }
+                        if (have_next) {
+                            tma_store_wait_read<0>();
+                            mbar_arrive_expect_tx(cfull_bar(buf ^ 1u), Cfg::EPI_BYTES);
+                            tma_load_2d(epi_base + (buf ^ 1u) * Cfg::EPI_BYTES, &tmC, nm0, nn0,
+                                        cfull_bar(buf ^ 1u));
+                        }
+                    } else {
+                        tma_store_wait_read<1>();
+                    }
+                }
+                if (has_c) {
+                    ok = ok && mbar_wait(cfull_bar(buf), (g >> 1) & 1u, wc, kWaitCTile);
+                } else {
+                    named_bar_sync(1, 128);
+                }
+                ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld is warp-collective
+                if (ok) {
+                    uint32_t r[32];
+                    tmem_ld_32x32b_x32(tmem_base + lane_base + acc * kBN + j * Cfg::EPI_COLS, r);
+                    tmem_wait_ld();
+                    float* col = epi_gen + buf * (Cfg::EPI_BYTES / 4) + et;
+                    if (has_c) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            col[i * Cfg::BM] = fmaf(alpha, __uint_as_float(r[i]), beta * col[i * Cfg::BM]);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) col[i * Cfg::BM] = alpha * __uint_as_float(r[i]);
+                    }
+                    fence_proxy_async_smem();
+                }
+                fail = named_bar_or(2, 128, !ok);
+                if (fail) break;
+                if (elected) {
+                    tma_store_2d(&tmD, m0, out_n0 + j * Cfg::EPI_COLS, epi_base + buf * Cfg::EPI_BYTES);
+                    tma_store_commit();
+                }
+            }
+            if (fail) break;
+            // the accumulator has been read out: hand it back to the MMA issuer
+            tc_fence_before_sync();
+            if constexpr (kPair) {
+                mbar_arrive_cluster(tmem_empty_bar(acc), 0);
+            } else {
+                mbar_arrive(tmem_empty_bar(acc));
+            }
+        }
+        if (elected) tma_store_wait_all<0>();
+    }
+
+    // ---------------------------------------------------------------------- common exit
+    tc_fence_before_sync();
+    __syncthreads();
+    if (*abort_flag) {
+        // give bulk copies that may still be in flight towards this CTA time to land
+        const unsigned long long t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+    }
+    if constexpr (kPair) cluster_sync_all();
+    if (warp == 2) {
+        tc_fence_after_sync();
+        tmem_dealloc<kCtas>(tmem_base, Cfg::TMEM_COLS);
+    }
+}
+
+// D[m, n] = alpha * sum_s ws[m, n + s * n_stride] + beta * C[m, n]; ws column-major with ldw.
+// Four rows per thread (M-contiguous float4 when everything is 16-byte aligned).
+__global__ void gemm_splitk_reduce(const float* __restrict__ ws, long long ldw, int n_stride,
+                                   int split_k, int M, int N, float alpha, float beta,
+                                   const float* __restrict__ C, long long ldc, float* __restrict__ D,
+                                   long long ldd, int vec_ok) {
+    const long long quads_m = (M + 3) / 4;
+    const long long total = quads_m * N;
+    for (long long q = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; q < total;
+         q += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int n = static_cast<int>(q / quads_m);
+        const int m = static_cast<int>(q - n * quads_m) * 4;
+        if (vec_ok && m + 3 < M) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int s = 0; s < split_k; ++s) {
+                const float4 v = *reinterpret_cast<const float4*>(ws + (n + static_cast<long long>(s) * n_stride) * ldw + m);
+                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+            }
+            float4 out = make_float4(alpha * acc.x, alpha * acc.y, alpha * acc.z, alpha * acc.w);
+            if (beta != 0.0f) {
+                const float4 c = *reinterpret_cast<const float4*>(C + n * ldc + m);
+                out.x = fmaf(beta, c.x, out.x); out.y = fmaf(beta, c.y, out.y);
+                out.z = fmaf(beta, c.z, out.z); out.w = fmaf(beta, c.w, out.w);
+            }
+            *reinterpret_cast<float4*>(D + n * ldd + m) = out;
+        } else {
+            for (int i = 0; i < 4 && m + i < M; ++i) {
+                float acc = 0.f;
+                for (int s = 0; s < split_k; ++s) acc += ws[(n + static_cast<long long>(s) * n_stride) * ldw + m + i];
+                float out = alpha * acc;
+                if (beta != 0.0f) out = fmaf(beta, C[n * ldc + m + i], out);
+                D[n * ldd + m + i] = out;
+            }
+        }
+    }
+}
+
+}  // namespace b200

@@ -1,0 +1,64 @@
+// Declarations shared by the translation units of libb200wmma.so (host side only).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+
+#include "../../include/b200wmma.h"
+
+namespace b200 {
+
+// thread-local error text behind b200_last_error()
+void set_error(const std::string& msg);
+int fail(int status, const std::string& msg);
+int cuda_fail(cudaError_t e, const char* what);
+
+#define B200_CUDA_TRY(expr)                                  \
+    do {                                                     \
+        cudaError_t e__ = (expr);                            \
+        if (e__ != cudaSuccess) return cuda_fail(e__, #expr); \
+    } while (0)
+
+struct GemmProblem {
+    int transA, transB;
+    int64_t M, N, K;
+    float alpha, beta;
+    const void* A;
+    int64_t lda;
+    const void* B;
+    int64_t ldb;
+    const float* C;
+    int64_t ldc;
+    float* D;
+    int64_t ldd;
+};
+
+struct GemmPlan {
+    int tile_n;    // 64 / 128 / 256
+    int cta_pair;  // 1 or 2 CTAs per tile
+    int split_k;   // >= 1
+    int max_ctas;  // grid cap (0 = SM count)
+    int relay_release;
+    unsigned long long wait_budget_ns;
+};
+
+struct LaunchInfo {
+    int kernel, tile_n, split_k, ctas, cta_pair;
+};
+
+// Scratch needed for the plan's split-K partials, in bytes (0 when split_k == 1).
+size_t gemm_tcgen05_scratch_bytes(const GemmProblem& g, const GemmPlan& plan);
+
+// True when the TMA/tcgen05 kernel can take the problem (alignment, sizes).
+bool gemm_tcgen05_eligible(const GemmProblem& g, std::string* why);
+
+// Enqueue the tcgen05 GEMM (and the split-K reduction when plan.split_k > 1).
+int gemm_tcgen05_launch(const GemmProblem& g, const GemmPlan& plan, float* scratch, int* status_word,
+                        int sm_count, cudaStream_t stream, LaunchInfo* info);
+
+// Enqueue the plain shared-memory kernel: any shape, any alignment.
+int gemm_simple_launch(const GemmProblem& g, cudaStream_t stream, LaunchInfo* info);
+
+}  // namespace b200

@@ -1,0 +1,219 @@
+/*
+ * b200wmma.h -- C ABI of libb200wmma.so: the FP16 x FP16 -> FP32 tensor-core GEMM path of
+ * CUDAnative.jl's WMMA module, rebuilt for NVIDIA B200 (sm_100a).
+ *
+ * Every entry point is `extern "C"`, takes plain pointers and sizes, returns an int status
+ * (0 = B200_OK) and never throws.  Device work is enqueued on the caller's stream and the call
+ * returns immediately unless its comment says otherwise; buffers stay owned by the caller.
+ * Matrices follow the reference's CuArray convention: dense column-major with a leading
+ * dimension in ELEMENTS (src/device/array.jl:104 of the reference, linear column-major
+ * indexing); a "row-major" operand is the same memory read as its transpose.
+ *
+ * Reference citations below are paths inside the CUDAnative.jl source tree.
+ */
+#ifndef B200WMMA_H
+#define B200WMMA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------------------------------ */
+/* status codes                                                                                */
+/* ------------------------------------------------------------------------------------------ */
+enum {
+    B200_OK = 0,
+    B200_INVALID_ARG = 1,    /* bad dims / leading dimension / null or misaligned pointer        */
+    B200_UNSUPPORTED = 2,    /* legal request this build has no kernel for                       */
+    B200_CUDA_ERROR = 3,     /* a CUDA runtime / driver call failed; text in b200_last_error()   */
+    B200_DEVICE_TIMEOUT = 4, /* a bounded wait inside a kernel ran out; see b200_device_status() */
+    B200_NO_DEVICE = 5       /* no CUDA device, or the device is not compute capability 10.x     */
+};
+
+/* Layout tags: the reference's WMMA.ColMajor / WMMA.RowMajor (src/device/cuda/wmma.jl:313-338). */
+enum { B200_COL_MAJOR = 0, B200_ROW_MAJOR = 1 };
+
+/* Element tags: Float16 / Float32, the two WMMA element types (src/device/cuda/wmma.jl:11-37). */
+enum { B200_F16 = 0, B200_F32 = 1 };
+
+/* Fragment use: WMMA.MatrixA / MatrixB / Accumulator (src/device/cuda/wmma.jl:343-346). */
+enum { B200_MATRIX_A = 0, B200_MATRIX_B = 1, B200_ACCUMULATOR = 2 };
+
+/* Which instruction family backs the 16x16x16 unit. */
+enum {
+    B200_LOWER_WARP = 0,   /* warp-level mma.sync.m16n8k16 x2, register fragments               */
+    B200_LOWER_TCGEN05 = 1 /* CTA-level tcgen05.mma (M padded to 128), accumulator in TMEM      */
+};
+
+/* Kernel selector for b200_set_option(B200_OPT_FORCE_KERNEL). */
+enum {
+    B200_KERNEL_AUTO = 0,
+    B200_KERNEL_TCGEN05 = 1, /* TMA + tcgen05 pipeline; fails with UNSUPPORTED if not eligible   */
+    B200_KERNEL_SIMPLE = 2   /* plain shared-memory FP32-FMA kernel (any alignment, any shape)   */
+};
+
+enum {
+    B200_OPT_FORCE_KERNEL = 0,   /* one of B200_KERNEL_*                                          */
+    B200_OPT_MAX_CTAS = 1,       /* cap on the persistent grid (0 = one CTA per SM)               */
+    B200_OPT_WAIT_BUDGET_NS = 2, /* budget of every in-kernel barrier wait (default 2e9 ns)       */
+    B200_OPT_TILE_N = 3,         /* 0 = auto, else 64 / 128 / 256                                 */
+    B200_OPT_SPLIT_K = 4,        /* 0 = auto, 1 = off, n>1 = split the K loop n ways              */
+    B200_OPT_CTA_PAIR = 5,       /* 0 = auto, 1 = one-CTA tiles only, 2 = force 2-CTA tiles       */
+    B200_OPT_RELAY_RELEASE = 6   /* 2-CTA tiles: 1 = the leader's producer relays stage releases  */
+                                 /* to its peer instead of the MMA thread committing to both      */
+};
+
+typedef struct b200_handle b200_handle;
+typedef void* b200_stream; /* a cudaStream_t; NULL = the legacy default stream */
+
+/* ------------------------------------------------------------------------------------------ */
+/* library, handle, errors                                                                     */
+/* ------------------------------------------------------------------------------------------ */
+
+/* Text of the calling thread's most recent failure ("" if none).  Replaces the CuError /
+ * KernelException text the reference surfaces at its next API call (src/exceptions.jl:76-89). */
+const char* b200_last_error(void);
+const char* b200_status_string(int status);
+
+/* ABI version of this header (major*100 + minor). */
+int b200_version(void);
+
+/* Number of CUDA devices with compute capability 10.x; negative status on CUDA failure.
+ * Replaces CUDAnative.functional() (src/CUDAnative.jl:29-52) for this path. */
+int b200_device_count(void);
+
+/* Create / destroy the per-device handle: device status word, workspace for the host-buffer
+ * entry point, tensor-map cache.  Binds to the device's primary context, the one CUDAnative's
+ * device!() uses (src/init.jl:187-209).  One handle per host thread (or lock externally). */
+int b200_create(b200_handle** out, int device);
+int b200_destroy(b200_handle* h);
+
+int b200_set_option(b200_handle* h, int option, int64_t value);
+int b200_get_option(b200_handle* h, int option, int64_t* value);
+
+/* After the stream has been synchronised: what the kernels of this handle last wrote into the
+ * device status word.  code 0 = nothing; otherwise the id of the wait that ran out, the block
+ * it was in and a detail word.  Clears the word.  Plays the role of the reference's polled
+ * device exception flag (src/exceptions.jl:55-89, src/device/runtime.jl:18-31). */
+int b200_device_status(b200_handle* h, int* code, int* block, int* detail);
+
+/* Launches one warp that waits, with the given budget (1 us .. 1 s), on a barrier nothing ever
+ * signals.  After synchronising, b200_device_status() must report wait id 107: the check that a
+ * stuck pipeline ends in an error code and a usable context rather than a hang.  The reference's
+ * counterpart is its device exception flag test path (src/exceptions.jl:76-89). */
+int b200_selftest_bounded_wait(b200_handle* h, b200_stream stream, int64_t budget_ns);
+
+/* Properties of the last GEMM launched through this handle: kernel id (B200_KERNEL_*), tile_n,
+ * split_k, CTAs launched, CTAs per tile (1 or 2).  Any out pointer may be NULL. */
+int b200_last_launch(b200_handle* h, int* kernel, int* tile_n, int* split_k, int* ctas,
+                     int* cta_pair);
+
+/* ------------------------------------------------------------------------------------------ */
+/* tiled GEMM: D = alpha * op(A) * op(B) + beta * C                                            */
+/* ------------------------------------------------------------------------------------------ */
+
+/* The multi-tile form of WMMA.load_a/load_b/load_c -> WMMA.mma -> WMMA.store_d
+ * (src/device/cuda/wmma.jl:507-530, :558-583, :613-632) with the alpha/beta scaling the
+ * reference applies by broadcasting over fragments (src/device/cuda/wmma.jl:678-716).
+ *
+ *   op(A) is M x K, op(B) is K x N, C and D are M x N, all column-major, all DEVICE pointers.
+ *   transA = 0: A stored M x K column-major, lda >= M   (WMMA.ColMajor A)
+ *   transA = 1: A stored K x M column-major (= M x K row-major), lda >= K (WMMA.RowMajor A)
+ *   transB likewise for the K x N operand.
+ *   A, B: IEEE binary16.  C, D: binary32.  Products exact, accumulation in binary32,
+ *   alpha and beta applied in binary32 in the epilogue.
+ *   beta == 0: C is never read and may be NULL (WMMA.fill_c(0) case, wmma.jl:654-667).
+ *   D may alias C exactly (same pointer, same ld).  M, N >= 0; K >= 0 (K == 0: D = beta*C).
+ *
+ * The tcgen05 kernel needs 16-byte aligned pointers and leading dimensions (lda, ldb
+ * multiples of 8 elements; ldc, ldd multiples of 4); anything else runs on the simple kernel. */
+int b200_gemm_f16f32(b200_handle* h, b200_stream stream, int transA, int transB, int64_t M,
+                     int64_t N, int64_t K, float alpha, const void* A, int64_t lda, const void* B,
+                     int64_t ldb, float beta, const float* C, int64_t ldc, float* D, int64_t ldd);
+
+/* Same operation with HOST pointers (ideally page-locked): copies A, B and (beta != 0) C to the
+ * handle's device workspace, runs the GEMM, copies D back and synchronises before returning.
+ * This is the Array -> CuArray -> kernel -> Array(d_dev) round trip of the reference's examples
+ * (examples/wmma/high-level.jl:21-47) as one call.  Allocates workspace on first use. */
+int b200_gemm_f16f32_host(b200_handle* h, int transA, int transB, int64_t M, int64_t N, int64_t K,
+                          float alpha, const void* A, int64_t lda, const void* B, int64_t ldb,
+                          float beta, const float* C, int64_t ldc, float* D, int64_t ldd);
+
+/* ------------------------------------------------------------------------------------------ */
+/* the 16x16x16 unit: one WMMA multiply-accumulate                                             */
+/* ------------------------------------------------------------------------------------------ */
+
+/* The whole body of the reference's example kernels (examples/wmma/high-level.jl:30-44,
+ * examples/wmma/low-level.jl:33-42) and of its high-level API test
+ * (test/device/wmma.jl:188-248) as one launch:
+ *     a = load_a(A); b = load_b(B); c = mac ? load_c(C) : fill_c(0)
+ *     a = alpha .* a   (rounded to Float16, as the fragment is Float16)
+ *     c = beta  .* c   (in C's element type)
+ *     d = mma(a, b, c); store_d(D, d)
+ * A, B: 16x16 binary16 with the given layouts and leading dimensions; C / D: binary16 or
+ * binary32.  `lowering` is B200_LOWER_WARP or B200_LOWER_TCGEN05.  use_alpha / use_beta = 0
+ * skip the corresponding broadcast entirely.  The tcgen05 lowering synchronises the stream
+ * before it returns, so that a bounded wait that ran out comes back as B200_DEVICE_TIMEOUT. */
+int b200_wmma_16x16x16(b200_stream stream, int lowering, int a_layout, int b_layout, int c_layout,
+                       int d_layout, int c_type, int d_type, int mac, int use_alpha, float alpha,
+                       int use_beta, float beta, const void* A, int64_t lda, const void* B,
+                       int64_t ldb, const void* C, int64_t ldc, void* D, int64_t ldd);
+
+/* Fragment-granular forms.  A fragment is the per-lane register image of one warp, kept in
+ * device memory as 32 lanes x FS elements (FS = 16 for A/B, 8 for C/D: src/device/cuda/wmma.jl:
+ * 413-420).  Which matrix element sits in which lane slot is private to this library, as the
+ * reference leaves it unspecified (docs/src/device/wmma.md:47-49).
+ *
+ * b200_wmma_load  : WMMA.load_a / load_b / load_c   (wmma.jl:507-530); use = B200_MATRIX_*.
+ * b200_wmma_fill_c: WMMA.fill_c                      (wmma.jl:654-667)
+ * b200_wmma_bcast : `s .* frag` / `s .+ frag`        (wmma.jl:678-716); op 0 = mul, 1 = add;
+ *                   computed in the fragment's element type.
+ * b200_wmma_mma   : WMMA.mma                         (wmma.jl:558-583)
+ * b200_wmma_store_d: WMMA.store_d                    (wmma.jl:613-632) */
+int b200_wmma_load(b200_stream stream, int use, int layout, int elem_type, const void* addr,
+                   int64_t stride, void* frag);
+int b200_wmma_fill_c(b200_stream stream, int elem_type, float value, void* frag);
+int b200_wmma_bcast(b200_stream stream, int op, int elem_type, int frag_size, float scalar,
+                    const void* frag_in, void* frag_out);
+int b200_wmma_mma(b200_stream stream, int c_type, int d_type, const void* a_frag,
+                  const void* b_frag, const void* c_frag, void* d_frag);
+int b200_wmma_store_d(b200_stream stream, int layout, int elem_type, void* addr, const void* frag,
+                      int64_t stride);
+
+/* ------------------------------------------------------------------------------------------ */
+/* device memory and synthetic inputs                                                          */
+/* ------------------------------------------------------------------------------------------ */
+
+/* What CUDAnative.CuHostArray does around a kernel (src/array.jl:20-60): allocate, upload,
+ * download, free.  b200_host_alloc returns page-locked host memory. */
+int b200_malloc(void** dptr, size_t bytes);
+int b200_free(void* dptr);
+int b200_host_alloc(void** hptr, size_t bytes);
+int b200_host_free(void* hptr);
+int b200_memcpy_h2d(void* dst, const void* src, size_t bytes, b200_stream stream);
+int b200_memcpy_d2h(void* dst, const void* src, size_t bytes, b200_stream stream);
+int b200_memset(void* dst, int byte, size_t bytes, b200_stream stream);
+int b200_stream_sync(b200_stream stream);
+
+/* Counter-based synthetic matrices (no counterpart in the reference, whose tests draw from
+ * Julia's unseeded rand; test/device/wmma.jl:196-199).  Element (i, j) of a rows x cols
+ * column-major matrix gets
+ *     u = splitmix64(seed * 0x9E3779B97F4A7C15 + matrix_id * 0xD1B54A32D192ED03 + index0 + (j*rows + i))
+ * (index0 = linear index of this window's first element inside a larger synthetic matrix of the
+ * same height: col0 * rows for a slab that starts at column col0, 0 for a whole matrix)
+ * dist 0: uniform[-1,1) = (u >> 40) * 2^-23 - 1
+ * dist 1: normal(0,1) by Box-Muller on the two 24-bit halves of u's top 48 bits
+ * dist 2: zeros
+ * times `scale`, then (f16 variant) rounded to nearest-even binary16. */
+int b200_fill_f16(b200_stream stream, void* dptr, int64_t rows, int64_t cols, int64_t ld,
+                  uint64_t seed, uint64_t matrix_id, uint64_t index0, int dist, float scale);
+int b200_fill_f32(b200_stream stream, float* dptr, int64_t rows, int64_t cols, int64_t ld,
+                  uint64_t seed, uint64_t matrix_id, uint64_t index0, int dist, float scale);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200WMMA_H */

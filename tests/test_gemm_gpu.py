@@ -1,0 +1,245 @@
+"""Parity of the tiled GEMM (through the C ABI) with the CPU oracle.
+
+Tolerances are BASELINE's: relative Frobenius error <= 1e-3 and |D - ref| <= 1e-2 * (|ref| + 1)
+elementwise, against float32 sgemm on the Float16-rounded inputs (oracle.assert_close)."""
+import numpy as np
+import pytest
+
+from cudanative_jl_b200 import _lib, rng
+from cudanative_jl_b200.array import Array, CuArray, CuHostArray
+from helpers import operands, padded, run_gemm
+
+pytestmark = pytest.mark.gpu
+
+LAYOUTS = [(False, False), (True, False), (False, True), (True, True)]
+
+
+def force(handle, kernel=_lib.KERNEL_TCGEN05, tile_n=0, pair=0, split_k=0, relay=0, max_ctas=0):
+    handle.set_option(_lib.OPT_FORCE_KERNEL, kernel)
+    handle.set_option(_lib.OPT_TILE_N, tile_n)
+    handle.set_option(_lib.OPT_CTA_PAIR, pair)
+    handle.set_option(_lib.OPT_SPLIT_K, split_k)
+    handle.set_option(_lib.OPT_RELAY_RELEASE, relay)
+    handle.set_option(_lib.OPT_MAX_CTAS, max_ctas)
+
+
+def test_simple_kernel_matches_oracle(handle, oracle):
+    """The plain kernel is the on-device yardstick for the big cases below: pin it first."""
+    force(handle, _lib.KERNEL_SIMPLE)
+    for (tA, tB) in LAYOUTS:
+        M, N, K = 150, 70, 99
+        a, b, c = operands(M, N, K, tA, tB, seed=11)
+        d = run_gemm(handle, tA, tB, M, N, K, 1.5, a, b, -0.5, c)
+        oracle.assert_close(d, oracle.gemm_ref(tA, tB, 1.5, a, b, -0.5, c), f"simple tA={tA} tB={tB}")
+        ref64 = oracle.gemm_c(tA, tB, 1.5, a.astype(np.float32), b.astype(np.float32), -0.5, c, True)
+        oracle.assert_close(d, ref64, "simple vs double accumulation")
+
+
+@pytest.mark.parametrize("tA,tB", LAYOUTS)
+@pytest.mark.parametrize("tile_n,pair", [(256, 1), (128, 1), (64, 1), (256, 2), (128, 2)])
+def test_one_tile_one_kblock(handle, oracle, tA, tB, tile_n, pair):
+    """Smallest case that exercises descriptors and TMEM layout: one tile, K = 64."""
+    if tB and (tile_n // pair) % 64:
+        pytest.skip("row-major B needs 64 tile columns per CTA")
+    force(handle, tile_n=tile_n, pair=pair)
+    M, N, K = 128 * pair, tile_n, 64
+    a, b, c = operands(M, N, K, tA, tB, seed=21)
+    d = run_gemm(handle, tA, tB, M, N, K, 1.0, a, b, 1.0, c)
+    oracle.assert_close(d, oracle.gemm_ref(tA, tB, 1.0, a, b, 1.0, c), f"one tile {tile_n}x{pair}")
+    info = handle.last_launch()
+    assert info["kernel"] == _lib.KERNEL_TCGEN05 and info["tile_n"] == tile_n and info["cta_pair"] == pair
+
+
+@pytest.mark.parametrize("tA,tB", LAYOUTS)
+@pytest.mark.parametrize("tile_n,pair", [(256, 1), (128, 1), (64, 1), (256, 2), (128, 2)])
+def test_ragged_multi_tile(handle, oracle, tA, tB, tile_n, pair):
+    """Several tiles per CTA pipeline, ragged M / N / K edges, alpha and beta both active."""
+    if tB and (tile_n // pair) % 64:
+        pytest.skip("row-major B needs 64 tile columns per CTA")
+    force(handle, tile_n=tile_n, pair=pair, max_ctas=6)  # few CTAs: each walks many tiles
+    M, N, K = 712, 664, 1000
+    a, b, c = operands(M, N, K, tA, tB, seed=31)
+    d = run_gemm(handle, tA, tB, M, N, K, 2.0, a, b, 0.5, c)
+    oracle.assert_close(d, oracle.gemm_ref(tA, tB, 2.0, a, b, 0.5, c), f"ragged {tile_n}x{pair}")
+
+
+@pytest.mark.parametrize("relay", [0, 1])
+def test_pair_release_modes(handle, oracle, relay):
+    """Both ways of releasing the peer CTA's stages give the same (bit-identical) result."""
+    force(handle, tile_n=256, pair=2, relay=relay)
+    M, N, K = 1024, 768, 2048
+    a, b, c = operands(M, N, K, True, False, seed=41)
+    d = run_gemm(handle, True, False, M, N, K, 1.0, a, b, 1.0, c)
+    oracle.assert_close(d, oracle.gemm_ref(True, False, 1.0, a, b, 1.0, c), f"pair relay={relay}")
+
+
+def test_beta_zero_never_reads_c(handle, oracle):
+    """beta == 0: C may be NULL (fill_c(0) case) and NaNs in a passed C must not leak."""
+    force(handle)
+    M, N, K = 256, 384, 320
+    a, b, c = operands(M, N, K, False, False, seed=51)
+    ref = oracle.gemm_ref(False, False, 3.0, a, b, 0.0, None)
+    oracle.assert_close(run_gemm(handle, False, False, M, N, K, 3.0, a, b, 0.0, None), ref, "C = NULL")
+    poison = np.full_like(c, np.nan)
+    oracle.assert_close(run_gemm(handle, False, False, M, N, K, 3.0, a, b, 0.0, poison), ref, "C = NaN")
+
+
+def test_d_aliases_c_and_padding_untouched(handle, oracle):
+    """In-place update (D is C) with ldd > M: rows M..ldd-1 must keep their canary values."""
+    force(handle)
+    M, N, K, ld = 200, 136, 192, 208
+    a, b, c = operands(M, N, K, False, False, seed=61)
+    cd = padded(c, ld, fill=np.float32(123.5))
+    cd_dev = CuArray(cd)
+    a_dev, b_dev = CuArray(a), CuArray(b)
+    handle.gemm(False, False, M, N, K, 1.0, a_dev, M, b_dev, K, 1.0, cd_dev, ld, cd_dev, ld)
+    out = Array(cd_dev)
+    assert handle.device_status()[0] == 0
+    oracle.assert_close(out[:M], oracle.gemm_ref(False, False, 1.0, a, b, 1.0, c), "in place")
+    assert np.all(out[M:] == np.float32(123.5)), "padding rows were overwritten"
+
+
+@pytest.mark.parametrize("split_k", [2, 3, 8])
+def test_split_k(handle, oracle, split_k):
+    force(handle, tile_n=128, pair=1, split_k=split_k)
+    M, N, K = 384, 128, 1536 + 40
+    a, b, c = operands(M, N, K, False, False, seed=71)
+    d = run_gemm(handle, False, False, M, N, K, 1.25, a, b, 0.75, c)
+    oracle.assert_close(d, oracle.gemm_ref(False, False, 1.25, a, b, 0.75, c), f"split_k={split_k}")
+    assert handle.last_launch()["split_k"] == split_k
+
+
+def test_unaligned_and_empty_shapes_take_the_simple_kernel(handle, oracle):
+    force(handle, _lib.KERNEL_AUTO)
+    # lda = 45 is not a multiple of 8: TMA cannot address it
+    M, N, K = 45, 37, 29
+    a, b, c = operands(M, N, K, False, False, seed=81)
+    d = run_gemm(handle, False, False, M, N, K, 1.0, a, b, 1.0, c)
+    oracle.assert_close(d, oracle.gemm_ref(False, False, 1.0, a, b, 1.0, c), "unaligned")
+    assert handle.last_launch()["kernel"] == _lib.KERNEL_SIMPLE
+    # K == 0: D = beta * C
+    c0 = rng.matrix(82, 2, 64, 32, rng.UNIFORM, 1.0, np.float32)
+    a0 = np.zeros((64, 0), np.float16, order="F")
+    b0 = np.zeros((0, 32), np.float16, order="F")
+    d0_dev, c0_dev = CuHostArray(np.float32, shape=(64, 32)), CuArray(c0)
+    handle.gemm(False, False, 64, 32, 0, 1.0, CuArray(np.zeros((1, 1), np.float16)), 64, CuArray(np.zeros((1, 1), np.float16)), 1,
+                0.5, c0_dev, 64, d0_dev, 64)
+    assert np.array_equal(Array(d0_dev), np.float32(0.5) * c0)
+    # M == 0 or N == 0: nothing to do, no error
+    handle.gemm(False, False, 0, 32, 16, 1.0, None, 1, None, 16, 0.0, None, 1, None, 1)
+    # forcing the tcgen05 kernel on an unaligned problem is refused loudly
+    force(handle, _lib.KERNEL_TCGEN05)
+    with pytest.raises(Exception, match="not eligible"):
+        run_gemm(handle, False, False, M, N, K, 1.0, a, b, 1.0, c)
+
+
+def test_argument_validation(handle):
+    with pytest.raises(Exception, match="lda smaller"):
+        handle.gemm(False, False, 64, 64, 64, 1.0, 256, 8, 256, 64, 0.0, None, 64, 256, 64)
+    with pytest.raises(Exception, match="C is null"):
+        handle.gemm(False, False, 64, 64, 64, 1.0, 256, 64, 256, 64, 1.0, None, 64, 256, 64)
+    with pytest.raises(Exception, match="negative"):
+        handle.gemm(False, False, -1, 64, 64, 1.0, 256, 64, 256, 64, 0.0, None, 64, 256, 64)
+
+
+def test_deterministic(handle):
+    force(handle, _lib.KERNEL_AUTO)
+    M, N, K = 1024, 1024, 1024
+    a, b, c = operands(M, N, K, False, False, seed=91)
+    d1 = run_gemm(handle, False, False, M, N, K, 1.0, a, b, 1.0, c)
+    d2 = run_gemm(handle, False, False, M, N, K, 1.0, a, b, 1.0, c)
+    assert np.array_equal(d1, d2)
+
+
+def test_config2_4096_cubed(handle, oracle):
+    """BASELINE config 2: M=N=K=4096, A, B column-major normal/sqrt(K), C normal, alpha=beta=1, seed 1."""
+    force(handle, _lib.KERNEL_AUTO)
+    n = 4096
+    a = rng.matrix(1, 0, n, n, rng.NORMAL, n ** -0.5, np.float16)
+    b = rng.matrix(1, 1, n, n, rng.NORMAL, n ** -0.5, np.float16)
+    c = rng.matrix(1, 2, n, n, rng.NORMAL, 1.0, np.float32)
+    d = run_gemm(handle, False, False, n, n, n, 1.0, a, b, 1.0, c)
+    assert handle.last_launch()["kernel"] == _lib.KERNEL_TCGEN05
+    oracle.assert_close(d, oracle.gemm_ref(False, False, 1.0, a, b, 1.0, c), "config 2")
+
+
+def test_config4_skinny(handle, oracle):
+    """BASELINE config 4: M=16384, N=128, K=8192, A column-major normal/sqrt(K), B normal, C zeros, beta=0, seed 3."""
+    force(handle, _lib.KERNEL_AUTO)
+    M, N, K = 16384, 128, 8192
+    a = rng.matrix(3, 0, M, K, rng.NORMAL, K ** -0.5, np.float16)
+    b = rng.matrix(3, 1, K, N, rng.NORMAL, 1.0, np.float16)
+    d = run_gemm(handle, False, False, M, N, K, 1.0, a, b, 0.0, None)
+    oracle.assert_close(d, oracle.gemm_ref(False, False, 1.0, a, b, 0.0, None), "config 4")
+
+
+def _device_problem(handle, M, N, K, seed, transA, c_dist):
+    """Operands generated on the device (too big to build on the host quickly)."""
+    L = _lib.lib()
+    a = CuHostArray(np.float16, shape=((K, M) if transA else (M, K)))
+    b = CuHostArray(np.float16, shape=(K, N))
+    c = CuHostArray(np.float32, shape=(M, N))
+    rng.fill_device(a.ptr, a.shape[0], a.shape[1], a.shape[0], seed, 0, rng.NORMAL, K ** -0.5, True)
+    rng.fill_device(b.ptr, K, N, K, seed, 1, rng.NORMAL, K ** -0.5, True)
+    rng.fill_device(c.ptr, M, N, M, seed, 2, c_dist, 1.0, False)
+    return a, b, c
+
+
+def test_config3_8192_cubed_properties(handle, oracle):
+    """BASELINE config 3 at full size: A row-major, B column-major, alpha=2, beta=0.5, seed 2.
+    Checked three ways without a full CPU product: (1) against the independent plain kernel on
+    the device, elementwise over the whole matrix; (2) sampled 128x128 tiles against the CPU
+    oracle with operands regenerated from the counter-based generator; (3) linearity in alpha."""
+    n = 8192
+    a, b, c = _device_problem(handle, n, n, n, 2, True, rng.UNIFORM)
+    d = CuHostArray(np.float32, shape=(n, n))
+    force(handle, _lib.KERNEL_AUTO)
+    handle.gemm(True, False, n, n, n, 2.0, a, n, b, n, 0.5, c, n, d, n)
+    d_host = Array(d)
+    assert handle.device_status()[0] == 0
+    assert handle.last_launch()["kernel"] == _lib.KERNEL_TCGEN05
+    # (2) sampled tiles vs CPU oracle
+    picks = [(0, 0), (n - 128, n - 128), (3968, 4224), (128 * 17, 128 * 45), (128 * 63, 0)]
+    for (m0, n0) in picks:
+        a_win = rng.window(2, 0, n, 0, n, m0, m0 + 128, rng.NORMAL, n ** -0.5, np.float16)  # stored K x M
+        b_win = rng.window(2, 1, n, 0, n, n0, n0 + 128, rng.NORMAL, n ** -0.5, np.float16)
+        c_win = rng.window(2, 2, n, m0, m0 + 128, n0, n0 + 128, rng.UNIFORM, 1.0, np.float32)
+        ref = oracle.gemm_ref(True, False, 2.0, a_win, b_win, 0.5, c_win)
+        oracle.assert_close(d_host[m0:m0 + 128, n0:n0 + 128], ref, f"config 3 tile ({m0},{n0})")
+    # (1) whole matrix vs the plain kernel
+    d2 = CuHostArray(np.float32, shape=(n, n))
+    force(handle, _lib.KERNEL_SIMPLE)
+    handle.gemm(True, False, n, n, n, 2.0, a, n, b, n, 0.5, c, n, d2, n)
+    oracle.assert_close(d_host, Array(d2), "config 3 vs plain kernel")
+    # (3) linearity: D(alpha=4, beta=0) == 2 * D(alpha=2, beta=0) exactly (powers of two)
+    force(handle, _lib.KERNEL_AUTO)
+    handle.gemm(True, False, n, n, n, 2.0, a, n, b, n, 0.0, None, n, d, n)
+    handle.gemm(True, False, n, n, n, 4.0, a, n, b, n, 0.0, None, n, d2, n)
+    assert np.array_equal(Array(d2), np.float32(2.0) * Array(d))
+
+
+def test_bounded_wait_reports_and_context_survives(handle, oracle):
+    """A wait nothing satisfies runs out after its budget, the status word names it, and the
+    context is still usable afterwards."""
+    L = _lib.lib()
+    _lib.check(L.b200_selftest_bounded_wait(handle._h, None, 2_000_000), "selftest")
+    _lib.check(L.b200_stream_sync(None), "sync")
+    code, block, _ = handle.device_status()
+    assert code == 107 and block == 0
+    assert handle.device_status()[0] == 0  # reading clears it
+    force(handle, _lib.KERNEL_AUTO)
+    a, b, c = operands(128, 128, 128, False, False, seed=5)
+    d = run_gemm(handle, False, False, 128, 128, 128, 1.0, a, b, 1.0, c)
+    oracle.assert_close(d, oracle.gemm_ref(False, False, 1.0, a, b, 1.0, c), "after timeout")
+
+
+def test_host_buffer_entry_point(handle, oracle):
+    """b200_gemm_f16f32_host: host in, host out, with a padded D window."""
+    force(handle, _lib.KERNEL_AUTO)
+    M, N, K = 512, 384, 256
+    a, b, c = operands(M, N, K, True, False, seed=95)
+    d = np.full((M + 8, N), np.float32(9.0), dtype=np.float32, order="F")
+    cp = padded(c, M + 8, fill=np.float32(0.0))
+    handle.gemm_host(True, False, M, N, K, 2.0, a, K, b, K, 0.5, cp, M + 8, d, M + 8)
+    oracle.assert_close(d[:M], oracle.gemm_ref(True, False, 2.0, a, b, 0.5, c), "host path")
+    assert np.all(d[M:] == np.float32(9.0))
