@@ -53,6 +53,7 @@ struct b200_handle {
     int split_k = 0;
     int cta_pair = 0;
     int relay_release = 0;
+    int raster_group = 0;
     // workspace of the host-buffer entry point and split-K scratch (grown on demand)
     void* ws[4] = {nullptr, nullptr, nullptr, nullptr};
     size_t ws_bytes[4] = {0, 0, 0, 0};
@@ -99,6 +100,7 @@ GemmPlan make_plan(const b200_handle* h, const GemmProblem& g) {
     GemmPlan plan;
     plan.max_ctas = h->max_ctas;
     plan.relay_release = h->relay_release;
+    plan.raster_group = h->raster_group;
     plan.wait_budget_ns = h->wait_budget_ns;
     int tile_n = h->tile_n;
     if (tile_n == 0) tile_n = g.N > 128 ? 256 : (g.N > 64 ? 128 : 64);
@@ -249,6 +251,10 @@ int b200_set_option(b200_handle* h, int option, int64_t value) {
         case B200_OPT_RELAY_RELEASE:
             h->relay_release = value ? 1 : 0;
             return B200_OK;
+        case B200_OPT_RASTER_GROUP:
+            if (value < 0 || value > 4096) return fail(B200_INVALID_ARG, "raster group must be in [0, 4096]");
+            h->raster_group = static_cast<int>(value);
+            return B200_OK;
         default:
             return fail(B200_INVALID_ARG, "unknown option");
     }
@@ -264,6 +270,7 @@ int b200_get_option(b200_handle* h, int option, int64_t* value) {
         case B200_OPT_SPLIT_K: *value = h->split_k; return B200_OK;
         case B200_OPT_CTA_PAIR: *value = h->cta_pair; return B200_OK;
         case B200_OPT_RELAY_RELEASE: *value = h->relay_release; return B200_OK;
+        case B200_OPT_RASTER_GROUP: *value = h->raster_group; return B200_OK;
         default: return fail(B200_INVALID_ARG, "unknown option");
     }
 }

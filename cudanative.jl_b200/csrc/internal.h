@@ -41,6 +41,7 @@ struct GemmPlan {
     int split_k;   // >= 1
     int max_ctas;  // grid cap (0 = SM count)
     int relay_release;
+    int raster_group;  // 0 = default
     unsigned long long wait_budget_ns;
 };
 
