@@ -18,7 +18,7 @@ MATRIX_A, MATRIX_B, ACCUMULATOR = 0, 1, 2
 LOWER_WARP, LOWER_TCGEN05 = 0, 1
 KERNEL_AUTO, KERNEL_TCGEN05, KERNEL_SIMPLE = 0, 1, 2
 (OPT_FORCE_KERNEL, OPT_MAX_CTAS, OPT_WAIT_BUDGET_NS, OPT_TILE_N, OPT_SPLIT_K, OPT_CTA_PAIR,
- OPT_RELAY_RELEASE, OPT_RASTER_GROUP) = range(8)
+ OPT_RASTER_GROUP) = range(7)
 
 _i, _i64, _u64, _f, _p, _sz = C.c_int, C.c_int64, C.c_uint64, C.c_float, C.c_void_p, C.c_size_t
 _pp = C.POINTER(C.c_void_p)

@@ -52,7 +52,6 @@ struct b200_handle {
     int tile_n = 0;
     int split_k = 0;
     int cta_pair = 0;
-    int relay_release = 0;
     int raster_group = 0;
     // workspace of the host-buffer entry point and split-K scratch (grown on demand)
     void* ws[4] = {nullptr, nullptr, nullptr, nullptr};
@@ -99,7 +98,6 @@ int validate(const GemmProblem& g) {
 GemmPlan make_plan(const b200_handle* h, const GemmProblem& g) {
     GemmPlan plan;
     plan.max_ctas = h->max_ctas;
-    plan.relay_release = h->relay_release;
     plan.raster_group = h->raster_group;
     plan.wait_budget_ns = h->wait_budget_ns;
     int tile_n = h->tile_n;
@@ -248,9 +246,6 @@ int b200_set_option(b200_handle* h, int option, int64_t value) {
             if (value < 0 || value > 2) return fail(B200_INVALID_ARG, "cta_pair must be 0, 1 or 2");
             h->cta_pair = static_cast<int>(value);
             return B200_OK;
-        case B200_OPT_RELAY_RELEASE:
-            h->relay_release = value ? 1 : 0;
-            return B200_OK;
         case B200_OPT_RASTER_GROUP:
             if (value < 0 || value > 4096) return fail(B200_INVALID_ARG, "raster group must be in [0, 4096]");
             h->raster_group = static_cast<int>(value);
@@ -269,7 +264,6 @@ int b200_get_option(b200_handle* h, int option, int64_t* value) {
         case B200_OPT_TILE_N: *value = h->tile_n; return B200_OK;
         case B200_OPT_SPLIT_K: *value = h->split_k; return B200_OK;
         case B200_OPT_CTA_PAIR: *value = h->cta_pair; return B200_OK;
-        case B200_OPT_RELAY_RELEASE: *value = h->relay_release; return B200_OK;
         case B200_OPT_RASTER_GROUP: *value = h->raster_group; return B200_OK;
         default: return fail(B200_INVALID_ARG, "unknown option");
     }

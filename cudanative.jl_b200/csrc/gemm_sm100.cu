@@ -162,7 +162,6 @@ int gemm_tcgen05_launch(const GemmProblem& g, const GemmPlan& plan, float* scrat
     p.kb_total = q.kb_total;
     p.kb_per_split = q.kb_per_split;
     p.raster_group = plan.raster_group > 0 ? plan.raster_group : 8;
-    p.relay_release = plan.relay_release;
     p.status = status_word;
     p.wait_budget_ns = plan.wait_budget_ns;
 

@@ -39,7 +39,6 @@ struct GemmParams {
     int kb_per_split;      // ceil(kb_total / split_k)
     int raster_group;      // tiles_m per rasterisation group
     int out_n_stride;      // column offset between k-slices in the output map (split_k > 1)
-    int relay_release;     // pair kernels: 1 = release peer stages by a relayed arrive
     float alpha, beta;     // epilogue scalars (split_k > 1: 1 and 0)
     int* status;
     unsigned long long wait_budget_ns;
@@ -124,12 +123,12 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     if (threadIdx.x == 0) {
         *abort_flag = 0;
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(full_bar(s), kCtas);   // one arrive(+tx) per CTA of the tile
-            mbar_init(empty_bar(s), 1);      // one tcgen05.commit (or one relayed arrive)
+            mbar_init(full_bar(s), 1);       // the leader's arrive; it expects both CTAs' bytes
+            mbar_init(empty_bar(s), 1);      // one tcgen05.commit
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(tmem_full_bar(a), 1);
-            mbar_init(tmem_empty_bar(a), 128 * kCtas);
+            mbar_init(tmem_empty_bar(a), 4 * kCtas);  // one arrive per epilogue warp
         }
         for (int b = 0; b < Cfg::EPI_BUFS; ++b) mbar_init(cfull_bar(b), 1);
         fence_mbar_init();
@@ -170,13 +169,8 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1u;
-                    ok = mbar_wait<kPair>(empty_bar(s), ph ^ 1u, wc, kWaitEmptyStage);
+                    ok = mbar_wait<false>(empty_bar(s), ph ^ 1u, wc, kWaitEmptyStage);
                     if (!ok) break;
-                    if (kPair && p.relay_release && cta_rank == 0 && it >= STAGES) {
-                        // the leader's stage is free, hence the MMAs that read the peer's
-                        // copy of the stage are complete as well: pass the release on
-                        mbar_arrive_cluster(empty_bar(s), 1);
-                    }
                     const uint32_t sa = stages_base + s * Cfg::STAGE_BYTES;
                     const uint32_t sb = sa + Cfg::A_BYTES;
                     const int k0 = kb * Cfg::BK;
@@ -197,9 +191,13 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                             tma_load_2d(sb, &tmB, k0, nb0, fb);
                         }
                     } else {
-                        // both CTAs of the pair report their bytes to the leader's barrier
+                        // Both CTAs' loads complete on the leader's barrier.  Only the leader
+                        // arrives, expecting the bytes of both: a cluster-scope (remote) arrive
+                        // per k-block from the peer would cost a memory barrier each time.  The
+                        // peer's bytes may land before the leader's expect_tx; the phase cannot
+                        // complete before the leader's arrival, so that is harmless.
                         const uint32_t fb = mapa_shared(full_bar(s), 0);
-                        mbar_arrive_expect_tx_cluster(fb, Cfg::STAGE_BYTES);
+                        if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(s), 2 * Cfg::STAGE_BYTES);
                         if constexpr (kAMn) {
                             tma_load_2d_pair(sa, &tmA, m0, k0, fb);
                             tma_load_2d_pair(sa + 8192, &tmA, m0 + 64, k0, fb);
@@ -230,14 +228,14 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 unit_decode(unit, m0, n0, kb0, kb1, out_n0);
                 const uint32_t acc = ucount & 1u;
                 const uint32_t aph = (ucount >> 1) & 1u;
-                ok = mbar_wait<kPair>(tmem_empty_bar(acc), aph ^ 1u, wc, kWaitTmemEmpty);
+                ok = mbar_wait<false>(tmem_empty_bar(acc), aph ^ 1u, wc, kWaitTmemEmpty);
                 if (!ok) break;
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + acc * kBN;
                 for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1u;
-                    ok = mbar_wait<kPair>(full_bar(s), ph, wc, kWaitFullStage);
+                    ok = mbar_wait<false>(full_bar(s), ph, wc, kWaitFullStage);
                     if (!ok) break;
                     tc_fence_after_sync();
                     const uint32_t sa = stages_base + s * Cfg::STAGE_BYTES;
@@ -254,7 +252,7 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                         umma_f16<kCtas>(d_tmem, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
                     }
                     umma_commit<kCtas>(empty_bar(s));
-                    if (kPair && !p.relay_release) umma_commit<kCtas>(mapa_shared(empty_bar(s), 1));
+                    if constexpr (kPair) umma_commit<kCtas>(mapa_shared(empty_bar(s), 1));
                 }
                 if (!ok) break;
                 umma_commit<kCtas>(tmem_full_bar(acc));
@@ -287,7 +285,7 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             const int nchunks = chunks_of(n0);
             const uint32_t acc = ucount & 1u;
             const uint32_t aph = (ucount >> 1) & 1u;
-            bool ok = mbar_wait<kPair>(tmem_full_bar(acc), aph, wc, kWaitTmemFull);
+            bool ok = mbar_wait<false>(tmem_full_bar(acc), aph, wc, kWaitTmemFull);
             tc_fence_after_sync();
             for (int j = 0; j < nchunks; ++j, ++g) {
                 const uint32_t buf = g & 1u;
@@ -343,10 +341,10 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             if (fail) break;
             // the accumulator has been read out: hand it back to the MMA issuer
             tc_fence_before_sync();
-            if constexpr (kPair) {
-                mbar_arrive_cluster(tmem_empty_bar(acc), 0);
-            } else {
-                mbar_arrive(tmem_empty_bar(acc));
+            __syncwarp();
+            if (lane == 0) {
+                if constexpr (kPair) mbar_arrive_cluster(tmem_empty_bar(acc), 0);
+                else mbar_arrive(tmem_empty_bar(acc));
             }
         }
         if (elected) tma_store_wait_all<0>();

@@ -40,7 +40,6 @@ struct GemmPlan {
     int cta_pair;  // 1 or 2 CTAs per tile
     int split_k;   // >= 1
     int max_ctas;  // grid cap (0 = SM count)
-    int relay_release;
     int raster_group;  // 0 = default
     unsigned long long wait_budget_ns;
 };

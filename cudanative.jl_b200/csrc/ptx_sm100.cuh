@@ -115,7 +115,7 @@ enum : int {
 struct WaitCtx {
     volatile int* abort_flag;      // in shared memory; set once by whoever gives up first
     int* status;                   // 4 ints in global memory: {code, block, detail, spare}
-    unsigned long long budget_ns;  // how long one wait may spin
+    unsigned long long budget_ns;  // how long one wait may spin (see mbar_wait)
 };
 
 // Records the first failure of the grid in the status word and raises the CTA's abort flag.
@@ -131,18 +131,24 @@ static __device__ __noinline__ void report_timeout(const WaitCtx& w, int where, 
 // Bounded wait for phase `parity` of an mbarrier.  Returns false when the budget ran out or
 // another role of this CTA already gave up; the caller must then fall through to the kernel's
 // common exit (which frees TMEM).  Never spins unboundedly.
+//
+// The budget is counted on the SM's cycle counter (reading %globaltimer costs a large fraction of
+// a microsecond, which a producer that is one stage ahead would pay on every k-block) at two
+// cycles per nanosecond: with SM clocks between 1 and 2 GHz a wait gives up after one to two
+// times budget_ns.
 template <bool kCluster = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx& w,
                                           int where) {
     if (kCluster ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = global_timer_ns();
+    const long long t0 = clock64();
+    const long long budget_cycles = static_cast<long long>(w.budget_ns) * 2;
     uint32_t spins = 0;
     for (;;) {
         if (kCluster ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity))
             return true;
-        if ((++spins & 127u) == 0u) {
+        if ((++spins & 31u) == 0u) {
             if (*w.abort_flag) return false;
-            if (global_timer_ns() - t0 > w.budget_ns) {
+            if (clock64() - t0 > budget_cycles) {
                 report_timeout(w, where, static_cast<int>(parity));
                 return false;
             }

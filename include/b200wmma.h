@@ -62,9 +62,7 @@ enum {
     B200_OPT_TILE_N = 3,         /* 0 = auto, else 64 / 128 / 256                                 */
     B200_OPT_SPLIT_K = 4,        /* 0 = auto, 1 = off, n>1 = split the K loop n ways              */
     B200_OPT_CTA_PAIR = 5,       /* 0 = auto, 1 = one-CTA tiles only, 2 = force 2-CTA tiles       */
-    B200_OPT_RELAY_RELEASE = 6,  /* 2-CTA tiles: 1 = the leader's producer relays stage releases  */
-                                 /* to its peer instead of the MMA thread committing to both      */
-    B200_OPT_RASTER_GROUP = 7    /* tile rows per rasterisation group (0 = default)               */
+    B200_OPT_RASTER_GROUP = 6    /* tile rows per rasterisation group (0 = default)               */
 };
 
 typedef struct b200_handle b200_handle;

@@ -14,12 +14,11 @@ pytestmark = pytest.mark.gpu
 LAYOUTS = [(False, False), (True, False), (False, True), (True, True)]
 
 
-def force(handle, kernel=_lib.KERNEL_TCGEN05, tile_n=0, pair=0, split_k=0, relay=0, max_ctas=0):
+def force(handle, kernel=_lib.KERNEL_TCGEN05, tile_n=0, pair=0, split_k=0, max_ctas=0):
     handle.set_option(_lib.OPT_FORCE_KERNEL, kernel)
     handle.set_option(_lib.OPT_TILE_N, tile_n)
     handle.set_option(_lib.OPT_CTA_PAIR, pair)
     handle.set_option(_lib.OPT_SPLIT_K, split_k)
-    handle.set_option(_lib.OPT_RELAY_RELEASE, relay)
     handle.set_option(_lib.OPT_MAX_CTAS, max_ctas)
 
 
@@ -63,14 +62,14 @@ def test_ragged_multi_tile(handle, oracle, tA, tB, tile_n, pair):
     oracle.assert_close(d, oracle.gemm_ref(tA, tB, 2.0, a, b, 0.5, c), f"ragged {tile_n}x{pair}")
 
 
-@pytest.mark.parametrize("relay", [0, 1])
-def test_pair_release_modes(handle, oracle, relay):
-    """Both ways of releasing the peer CTA's stages give the same (bit-identical) result."""
-    force(handle, tile_n=256, pair=2, relay=relay)
+@pytest.mark.parametrize("tile_n", [128, 256])
+def test_pair_many_stage_wraps(handle, oracle, tile_n):
+    """2-CTA tiles with a K loop far longer than the stage ring and several tiles per pair."""
+    force(handle, tile_n=tile_n, pair=2, max_ctas=4)
     M, N, K = 1024, 768, 2048
     a, b, c = operands(M, N, K, True, False, seed=41)
     d = run_gemm(handle, True, False, M, N, K, 1.0, a, b, 1.0, c)
-    oracle.assert_close(d, oracle.gemm_ref(True, False, 1.0, a, b, 1.0, c), f"pair relay={relay}")
+    oracle.assert_close(d, oracle.gemm_ref(True, False, 1.0, a, b, 1.0, c), f"pair tile_n={tile_n}")
 
 
 def test_beta_zero_never_reads_c(handle, oracle):
