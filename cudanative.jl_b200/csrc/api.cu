@@ -103,7 +103,9 @@ GemmPlan make_plan(const b200_handle* h, const GemmProblem& g) {
     int tile_n = h->tile_n;
     if (tile_n == 0) tile_n = g.N > 128 ? 256 : (g.N > 64 ? 128 : 64);
     int pair = h->cta_pair;
-    if (pair == 0) pair = (g.M > 128 && tile_n >= 128) ? 2 : 1;
+    // 2-CTA tiles halve the B traffic per SM and pay off once the tile is 256 columns wide;
+    // narrow (HBM-bound) problems stream better with independent CTAs.
+    if (pair == 0) pair = (g.M > 128 && tile_n == 256) ? 2 : 1;
     if (pair == 2 && tile_n < 128) pair = 1;
     if (g.transB && (tile_n / pair) % 64) pair = 1;  // row-major B loads 64 columns per box
     plan.tile_n = tile_n;

@@ -160,17 +160,27 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            uint32_t it = 0;
+            int s = 0;          // stage of the ring
+            uint32_t ph = 0;    // its phase bit
             bool ok = true;
+#ifdef B200_PROBE_SKIP_LOADS
+            uint32_t issued = 0;
+#endif
             for (int unit = unit_first; ok && unit < num_units; unit += unit_stride) {
                 int m0, n0, kb0, kb1, out_n0;
                 unit_decode(unit, m0, n0, kb0, kb1, out_n0);
                 const int nb0 = n0 + static_cast<int>(cta_rank) * Cfg::BN_LOCAL;
-                for (int kb = kb0; kb < kb1; ++kb, ++it) {
-                    const int s = it % STAGES;
-                    const uint32_t ph = (it / STAGES) & 1u;
+                for (int kb = kb0; kb < kb1; ++kb, s = (s + 1 == STAGES ? 0 : s + 1), ph ^= (s == 0)) {
                     ok = mbar_wait<false>(empty_bar(s), ph ^ 1u, wc, kWaitEmptyStage);
                     if (!ok) break;
+#ifdef B200_PROBE_SKIP_LOADS
+                    // timing probe (results are wrong): after the ring has been filled once,
+                    // stages are handed back to the MMA without reloading them
+                    if (issued++ >= static_cast<uint32_t>(STAGES)) {
+                        if (cta_rank == 0) mbar_arrive(full_bar(s));
+                        continue;
+                    }
+#endif
                     const uint32_t sa = stages_base + s * Cfg::STAGE_BYTES;
                     const uint32_t sb = sa + Cfg::A_BYTES;
                     const int k0 = kb * Cfg::BK;
@@ -221,7 +231,18 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         if (lane == 0 && cta_rank == 0) {
             constexpr uint32_t idesc =
                 make_idesc_f16_f32(Cfg::BM * kCtas, kBN, kAMn ? 1 : 0, kBMn ? 1 : 0);
-            uint32_t it = 0, ucount = 0;
+            // Descriptors differ between stages and k-steps only in their start-address field
+            // (bits [0,14), in units of 16 bytes): build them once and add offsets.
+            // K-major tile: rows of 128 B, 8-row groups 1 KiB apart, k = 16 advances 32 B inside
+            // the swizzled row.  MN-major tile: 64 (m or n) x 64 k boxes of 8 KiB, 8-k groups
+            // 1 KiB apart, k = 16 advances 2 KiB.
+            const uint64_t da0 = kAMn ? make_smem_desc(stages_base, 8192, 1024, kSwizzle128B)
+                                      : make_smem_desc(stages_base, 16, 1024, kSwizzle128B);
+            const uint64_t db0 = kBMn ? make_smem_desc(stages_base + Cfg::A_BYTES, 8192, 1024, kSwizzle128B)
+                                      : make_smem_desc(stages_base + Cfg::A_BYTES, 16, 1024, kSwizzle128B);
+            constexpr uint32_t kStepA = (kAMn ? 2048 : 32) >> 4, kStepB = (kBMn ? 2048 : 32) >> 4;
+            int s = 0;
+            uint32_t ph = 0, ucount = 0;
             bool ok = true;
             for (int unit = unit_first; ok && unit < num_units; unit += unit_stride, ++ucount) {
                 int m0, n0, kb0, kb1, out_n0;
@@ -232,31 +253,34 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 if (!ok) break;
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + acc * kBN;
-                for (int kb = kb0; kb < kb1; ++kb, ++it) {
-                    const int s = it % STAGES;
-                    const uint32_t ph = (it / STAGES) & 1u;
+                uint32_t accumulate = 0;
+                for (int kb = kb0; kb < kb1; ++kb, s = (s + 1 == STAGES ? 0 : s + 1), ph ^= (s == 0)) {
                     ok = mbar_wait<false>(full_bar(s), ph, wc, kWaitFullStage);
                     if (!ok) break;
                     tc_fence_after_sync();
-                    const uint32_t sa = stages_base + s * Cfg::STAGE_BYTES;
-                    const uint32_t sb = sa + Cfg::A_BYTES;
+                    const uint64_t da = da0 + static_cast<uint64_t>(s * (Cfg::STAGE_BYTES >> 4));
+                    const uint64_t db = db0 + static_cast<uint64_t>(s * (Cfg::STAGE_BYTES >> 4));
 #pragma unroll
                     for (int k = 0; k < Cfg::BK / 16; ++k) {
-                        // K-major tile: rows of 128 B, 8-row groups 1 KiB apart, k advances
-                        // 32 B inside the swizzled row.  MN-major tile: 64 (m or n) x 64 k
-                        // boxes of 8 KiB, 8-k groups 1 KiB apart, k = 16 advances 2 KiB.
-                        const uint64_t da = kAMn ? make_smem_desc(sa + k * 2048, 8192, 1024, kSwizzle128B)
-                                                 : make_smem_desc(sa + k * 32, 16, 1024, kSwizzle128B);
-                        const uint64_t db = kBMn ? make_smem_desc(sb + k * 2048, 8192, 1024, kSwizzle128B)
-                                                 : make_smem_desc(sb + k * 32, 16, 1024, kSwizzle128B);
-                        umma_f16<kCtas>(d_tmem, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                        umma_f16<kCtas>(d_tmem, da + k * kStepA, db + k * kStepB, idesc, accumulate);
+                        accumulate = 1u;
                     }
+#ifdef B200_DOUBLE_COMMIT
                     umma_commit<kCtas>(empty_bar(s));
                     if constexpr (kPair) umma_commit<kCtas>(mapa_shared(empty_bar(s), 1));
+#else
+                    if constexpr (kPair) umma_commit_pair(empty_bar(s));
+                    else umma_commit<kCtas>(empty_bar(s));
+#endif
                 }
                 if (!ok) break;
+#ifdef B200_DOUBLE_COMMIT
                 umma_commit<kCtas>(tmem_full_bar(acc));
                 if constexpr (kPair) umma_commit<kCtas>(mapa_shared(tmem_full_bar(acc), 1));
+#else
+                if constexpr (kPair) umma_commit_pair(tmem_full_bar(acc));
+                else umma_commit<kCtas>(tmem_full_bar(acc));
+#endif
             }
         }
         __syncwarp();

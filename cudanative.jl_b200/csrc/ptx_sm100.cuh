@@ -371,6 +371,16 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
     }
 }
 
+// 2-CTA form that arrives on the barrier at offset `bar` in BOTH CTAs of the pair (CTA mask 0b11)
+// with one instruction.  This qualifier applies to the commit's barrier signal only; no load in
+// this library carries it.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+        "h"(static_cast<uint16_t>(3))
+        : "memory");
+}
+
 __device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t cta_rank) {
     uint32_t r;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(cta_rank));
