@@ -4,6 +4,8 @@
 #include <algorithm>
 #include <cstring>
 #include <string>
+#include <vector>
+#include <cuda_fp16.h>
 
 #include "internal.h"
 #include "ptx_sm100.cuh"
@@ -58,7 +60,8 @@ struct b200_handle {
     size_t ws_bytes[4] = {0, 0, 0, 0};
     float* scratch = nullptr;
     size_t scratch_bytes = 0;
-    cudaStream_t own_stream = nullptr;
+    cudaStream_t streams[3] = {nullptr, nullptr, nullptr};  // upload / multiply / download
+    std::vector<cudaEvent_t> events;
     LaunchInfo last = {0, 0, 0, 0, 0};
 };
 
@@ -216,7 +219,9 @@ int b200_destroy(b200_handle* h) {
         if (h->ws[i]) cudaFree(h->ws[i]);
     if (h->scratch) cudaFree(h->scratch);
     if (h->status_word) cudaFree(h->status_word);
-    if (h->own_stream) cudaStreamDestroy(h->own_stream);
+    for (int i = 0; i < 3; ++i)
+        if (h->streams[i]) cudaStreamDestroy(h->streams[i]);
+    for (cudaEvent_t e : h->events) cudaEventDestroy(e);
     delete h;
     return B200_OK;
 }
@@ -317,8 +322,9 @@ int b200_gemm_f16f32_host(b200_handle* h, int transA, int transB, int64_t M, int
     if (rc) return rc;
     if (M == 0 || N == 0) return B200_OK;
     B200_CUDA_TRY(cudaSetDevice(h->device));
-    if (!h->own_stream) B200_CUDA_TRY(cudaStreamCreateWithFlags(&h->own_stream, cudaStreamNonBlocking));
-    cudaStream_t s = h->own_stream;
+    for (int i = 0; i < 3; ++i)
+        if (!h->streams[i]) B200_CUDA_TRY(cudaStreamCreateWithFlags(&h->streams[i], cudaStreamNonBlocking));
+    cudaStream_t s_up = h->streams[0], s_mm = h->streams[1], s_dn = h->streams[2];
     const int64_t a_cols = transA ? M : K, b_cols = transB ? K : N;
     const bool has_c = (beta != 0.0f);
     const size_t a_bytes = static_cast<size_t>(lda) * a_cols * 2, b_bytes = static_cast<size_t>(ldb) * b_cols * 2;
@@ -327,22 +333,61 @@ int b200_gemm_f16f32_host(b200_handle* h, int transA, int transB, int64_t M, int
     if ((rc = ensure_buffer(&h->ws[1], &h->ws_bytes[1], std::max<size_t>(b_bytes, 16)))) return rc;
     if ((rc = ensure_buffer(&h->ws[2], &h->ws_bytes[2], std::max<size_t>(c_bytes, 16)))) return rc;
     if ((rc = ensure_buffer(&h->ws[3], &h->ws_bytes[3], std::max<size_t>(d_bytes, 16)))) return rc;
-    if (K > 0) {
-        B200_CUDA_TRY(cudaMemcpyAsync(h->ws[0], A, a_bytes, cudaMemcpyHostToDevice, s));
-        B200_CUDA_TRY(cudaMemcpyAsync(h->ws[1], B, b_bytes, cudaMemcpyHostToDevice, s));
+    __half* dA = static_cast<__half*>(h->ws[0]);
+    __half* dB = static_cast<__half*>(h->ws[1]);
+    float* dC = static_cast<float*>(h->ws[2]);
+    float* dD = static_cast<float*>(h->ws[3]);
+
+    // The link is full duplex and the GEMM is far faster than either direction, so the call is
+    // cut into column slabs: while slab j multiplies, slab j+1's B and C columns are still
+    // arriving and slab j-1's D columns are already on their way back.  A is needed by every
+    // slab and goes first.
+    int slabs = static_cast<int>(std::min<int64_t>(8, (N + 511) / 512));
+    if (slabs < 1) slabs = 1;
+    const int64_t per = ((N + slabs - 1) / slabs + 255) / 256 * 256;  // whole tiles per slab
+    while (static_cast<int>(h->events.size()) < 2 * slabs + 1) {
+        cudaEvent_t e;
+        B200_CUDA_TRY(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        h->events.push_back(e);
     }
-    if (has_c) B200_CUDA_TRY(cudaMemcpyAsync(h->ws[2], C, c_bytes, cudaMemcpyHostToDevice, s));
-    GemmProblem g{transA, transB, M, N, K, alpha, beta, h->ws[0], lda, h->ws[1], ldb,
-                  static_cast<const float*>(h->ws[2]), ldc, static_cast<float*>(h->ws[3]), ldd};
-    if ((rc = run_gemm(h, s, g))) return rc;
-    if (ldd == M) {
-        B200_CUDA_TRY(cudaMemcpyAsync(D, h->ws[3], static_cast<size_t>(M) * N * 4, cudaMemcpyDeviceToHost, s));
-    } else {
-        // only the M x N window of D belongs to the operation
-        B200_CUDA_TRY(cudaMemcpy2DAsync(D, static_cast<size_t>(ldd) * 4, h->ws[3], static_cast<size_t>(ldd) * 4,
-                                        static_cast<size_t>(M) * 4, static_cast<size_t>(N), cudaMemcpyDeviceToHost, s));
+    if (K > 0) B200_CUDA_TRY(cudaMemcpyAsync(dA, A, a_bytes, cudaMemcpyHostToDevice, s_up));
+    B200_CUDA_TRY(cudaEventRecord(h->events[0], s_up));
+    B200_CUDA_TRY(cudaStreamWaitEvent(s_mm, h->events[0], 0));
+    int j = 0;
+    for (int64_t n0 = 0; n0 < N; n0 += per, ++j) {
+        const int64_t nc = std::min<int64_t>(per, N - n0);
+        if (K > 0) {
+            if (!transB) {  // K x N column-major: a column slab is contiguous
+                B200_CUDA_TRY(cudaMemcpyAsync(dB + n0 * ldb, static_cast<const __half*>(B) + n0 * ldb,
+                                              static_cast<size_t>(ldb) * nc * 2, cudaMemcpyHostToDevice, s_up));
+            } else {        // stored N x K: rows n0 .. n0+nc of every column
+                B200_CUDA_TRY(cudaMemcpy2DAsync(dB + n0, static_cast<size_t>(ldb) * 2, static_cast<const __half*>(B) + n0,
+                                                static_cast<size_t>(ldb) * 2, static_cast<size_t>(nc) * 2,
+                                                static_cast<size_t>(K), cudaMemcpyHostToDevice, s_up));
+            }
+        }
+        if (has_c)
+            B200_CUDA_TRY(cudaMemcpyAsync(dC + n0 * ldc, C + n0 * ldc, static_cast<size_t>(ldc) * nc * 4,
+                                          cudaMemcpyHostToDevice, s_up));
+        B200_CUDA_TRY(cudaEventRecord(h->events[1 + 2 * j], s_up));
+        B200_CUDA_TRY(cudaStreamWaitEvent(s_mm, h->events[1 + 2 * j], 0));
+        GemmProblem g{transA, transB, M, nc, K, alpha, beta, dA, lda, transB ? dB + n0 : dB + n0 * ldb, ldb,
+                      dC + n0 * ldc, ldc, dD + n0 * ldd, ldd};
+        if ((rc = run_gemm(h, s_mm, g))) return rc;
+        B200_CUDA_TRY(cudaEventRecord(h->events[2 + 2 * j], s_mm));
+        B200_CUDA_TRY(cudaStreamWaitEvent(s_dn, h->events[2 + 2 * j], 0));
+        if (ldd == M) {
+            B200_CUDA_TRY(cudaMemcpyAsync(D + n0 * ldd, dD + n0 * ldd, static_cast<size_t>(M) * nc * 4,
+                                          cudaMemcpyDeviceToHost, s_dn));
+        } else {  // only the M x N window of D belongs to the operation
+            B200_CUDA_TRY(cudaMemcpy2DAsync(D + n0 * ldd, static_cast<size_t>(ldd) * 4, dD + n0 * ldd,
+                                            static_cast<size_t>(ldd) * 4, static_cast<size_t>(M) * 4,
+                                            static_cast<size_t>(nc), cudaMemcpyDeviceToHost, s_dn));
+        }
     }
-    B200_CUDA_TRY(cudaStreamSynchronize(s));
+    B200_CUDA_TRY(cudaStreamSynchronize(s_dn));
+    B200_CUDA_TRY(cudaStreamSynchronize(s_mm));
+    B200_CUDA_TRY(cudaStreamSynchronize(s_up));
     int word[4] = {0, 0, 0, 0};
     if ((rc = read_status(h, word))) return rc;
     if (word[0] != 0)

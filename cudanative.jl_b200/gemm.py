@@ -177,7 +177,7 @@ class ShardedGemm:
     """
 
     def __init__(self, handle: Handle, M: int, N: int, K: int, *, panels: int = 8, reserve_ctas: int = 8,
-                 group=None):
+                 group=None, sm_count: int | None = None):
         import torch
         import torch.distributed as dist
 
@@ -190,6 +190,9 @@ class ShardedGemm:
         self.n0, self.n1 = slab_bounds(N, self.world, self.rank)
         self.panels = panel_bounds(K, panels if self.world > 1 else 1)
         self.reserve_ctas = reserve_ctas if self.world > 1 else 0
+        if sm_count is None:
+            sm_count = torch.cuda.get_device_properties(handle.device).multi_processor_count
+        self.sm_count = sm_count
 
     @property
     def slab_cols(self) -> int:
@@ -218,15 +221,17 @@ class ShardedGemm:
         a_addr, b_addr = a_flat.data_ptr(), B_slab.data_ptr()
         c_addr = C_slab.data_ptr() if C_slab is not None else None
         d_addr = D_slab.data_ptr()
-        s = stream if stream is not None else torch.cuda.current_stream().cuda_stream
+        if stream is not None:
+            s = stream
+        else:
+            s = torch.cuda.current_stream().cuda_stream if a_flat.is_cuda else None
         try:
             for p, (k0, k1) in enumerate(self.panels):
                 last = p == len(self.panels) - 1
                 if works:
                     works[p].wait()  # stream-level: the GEMM below is ordered after panel p
                 if self.reserve_ctas and not last:
-                    sms = torch.cuda.get_device_properties(h.device).multi_processor_count
-                    h.set_option(_lib.OPT_MAX_CTAS, max(2, (sms - self.reserve_ctas) // 2 * 2))
+                    h.set_option(_lib.OPT_MAX_CTAS, max(2, (self.sm_count - self.reserve_ctas) // 2 * 2))
                 else:
                     h.set_option(_lib.OPT_MAX_CTAS, saved)
                 h.gemm(False, False, M, ns, k1 - k0, alpha, a_addr + 2 * k0 * M, M, b_addr + 2 * k0, K,

@@ -233,13 +233,19 @@ def test_bounded_wait_reports_and_context_survives(handle, oracle):
     oracle.assert_close(d, oracle.gemm_ref(False, False, 1.0, a, b, 1.0, c), "after timeout")
 
 
-def test_host_buffer_entry_point(handle, oracle):
-    """b200_gemm_f16f32_host: host in, host out, with a padded D window."""
+@pytest.mark.parametrize("tA,tB,N", [(True, False, 384), (False, True, 1300), (False, False, 2600)])
+def test_host_buffer_entry_point(handle, oracle, tA, tB, N):
+    """b200_gemm_f16f32_host: host in, host out; wide N is cut into column slabs whose uploads,
+    products and downloads overlap; D has padding rows that must stay untouched."""
     force(handle, _lib.KERNEL_AUTO)
-    M, N, K = 512, 384, 256
-    a, b, c = operands(M, N, K, True, False, seed=95)
+    M, K = 512, 256
+    a, b, c = operands(M, N, K, tA, tB, seed=95)
     d = np.full((M + 8, N), np.float32(9.0), dtype=np.float32, order="F")
     cp = padded(c, M + 8, fill=np.float32(0.0))
-    handle.gemm_host(True, False, M, N, K, 2.0, a, K, b, K, 0.5, cp, M + 8, d, M + 8)
-    oracle.assert_close(d[:M], oracle.gemm_ref(True, False, 2.0, a, b, 0.5, c), "host path")
+    handle.gemm_host(tA, tB, M, N, K, 2.0, a, a.shape[0], b, b.shape[0], 0.5, cp, M + 8, d, M + 8)
+    oracle.assert_close(d[:M], oracle.gemm_ref(tA, tB, 2.0, a, b, 0.5, c), "host path")
     assert np.all(d[M:] == np.float32(9.0))
+    # beta == 0 with no C at all
+    d2 = np.zeros((M, N), dtype=np.float32, order="F")
+    handle.gemm_host(tA, tB, M, N, K, 1.0, a, a.shape[0], b, b.shape[0], 0.0, None, M, d2, M)
+    oracle.assert_close(d2, oracle.gemm_ref(tA, tB, 1.0, a, b, 0.0, None), "host path, beta = 0")

@@ -1,0 +1,45 @@
+"""Host-side logic of the N-sharded GEMM: slab / panel arithmetic, and the whole ShardedGemm.run
+flow on two gloo ranks on the CPU with the CPU oracle standing in for the GEMM call."""
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+
+from cudanative_jl_b200.gemm import panel_bounds, slab_bounds
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+@pytest.mark.parametrize("n,world", [(32768, 8), (32768, 1), (1000, 3), (256, 4), (100, 8), (0, 2), (8192, 5)])
+def test_slabs_partition_the_columns(n, world):
+    bounds = [slab_bounds(n, world, r) for r in range(world)]
+    assert bounds[0][0] == 0 and bounds[-1][1] == n
+    for (a0, a1), (b0, b1) in zip(bounds, bounds[1:]):
+        assert a1 == b0 and a0 <= a1
+    for (n0, n1) in bounds:
+        assert n0 % 256 == 0 or n0 == n  # slabs start on tile boundaries
+    sizes = [n1 - n0 for (n0, n1) in bounds]
+    assert max(sizes) - min(sizes) <= 256 + 255  # as even as whole tiles allow
+
+
+@pytest.mark.parametrize("k,panels", [(16384, 8), (16384, 1), (1000, 4), (64, 8), (130, 3), (1, 2)])
+def test_panels_partition_k(k, panels):
+    b = panel_bounds(k, panels)
+    assert b[0][0] == 0 and b[-1][1] == k and len(b) <= panels
+    for (a0, a1), (b0, b1) in zip(b, b[1:]):
+        assert a1 == b0 and a1 > a0
+    assert all(k0 % 64 == 0 for (k0, _) in b)
+
+
+@pytest.mark.parametrize("world,shape", [(2, (96, 640, 200)), (3, (64, 512, 130))])
+def test_sharded_flow_on_gloo(world, shape):
+    """world ranks on the CPU: broadcast of A in K panels (gloo), per-panel accumulate calls with the
+    right pointer offsets, the SM reservation on all but the last panel, D slabs against the oracle."""
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+           "--master-port", str(29500 + world), str(ROOT / "tests" / "sharded_worker.py"), "gloo", *map(str, shape), "3"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count(" ok: slab") == world
