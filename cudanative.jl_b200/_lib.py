@@ -39,6 +39,7 @@ SIGNATURES = {
     "b200_last_launch": (_i, [_p, _ip, _ip, _ip, _ip, _ip]),
     "b200_gemm_f16f32": (_i, [_p, _p, _i, _i, _i64, _i64, _i64, _f, _p, _i64, _p, _i64, _f, _p, _i64, _p, _i64]),
     "b200_gemm_f16f32_host": (_i, [_p, _i, _i, _i64, _i64, _i64, _f, _p, _i64, _p, _i64, _f, _p, _i64, _p, _i64]),
+    "b200_gemm_f16f32_splitk_static": (_i, [_p, _i, _i, _i64, _i64, _i64, _f, _p, _i64, _p, _i64, _f, _p, _i64, _p, _i64, _i, _i]),
     "b200_wmma_16x16x16": (_i, [_p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _f, _p, _i64, _p, _i64, _p, _i64, _p, _i64]),
     "b200_wmma_load": (_i, [_p, _i, _i, _i, _p, _i64, _p]),
     "b200_wmma_fill_c": (_i, [_p, _i, _f, _p]),

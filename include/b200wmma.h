@@ -141,6 +141,25 @@ int b200_gemm_f16f32_host(b200_handle* h, int transA, int transB, int64_t M, int
                           float alpha, const void* A, int64_t lda, const void* B, int64_t ldb,
                           float beta, const float* C, int64_t ldc, float* D, int64_t ldd);
 
+/* The same product for callers that cannot allocate device memory when they need it (inside an
+ * allocator callback, in a loop that promised "no driver allocations after start-up", in a host
+ * that owns every byte of device memory).  No counterpart in the reference, which allocates
+ * freely through CUDAdrv.  Needs no handle and calls no cudaMalloc / cudaFree: the K loop is cut
+ * into `split_k` slices (2..64) whose FP32 partial products, and the device status word, live in
+ * a 16 MiB + 256 B array that is part of the library image on every GPU that loads it.
+ *   - The partials take roundup(M,4) * roundup(N, tile width) * slices * 4 bytes; a problem that
+ *     needs more than 16 MiB is refused with B200_INVALID_ARG (text in b200_last_error()).
+ *   - Same alignment rules as the TMA path of b200_gemm_f16f32; there is no fallback kernel.
+ *   - The first call on a device looks the array's address up; make it outside stream capture.
+ *   - All calls on a device share the array: calls that overlap on the GPU race.  Serialise them.
+ *   - sync_and_check != 0: synchronise the stream and return B200_DEVICE_TIMEOUT if a bounded
+ *     wait ran out; 0: return as soon as the work is enqueued. */
+int b200_gemm_f16f32_splitk_static(b200_stream stream, int transA, int transB, int64_t M,
+                                   int64_t N, int64_t K, float alpha, const void* A, int64_t lda,
+                                   const void* B, int64_t ldb, float beta, const float* C,
+                                   int64_t ldc, float* D, int64_t ldd, int split_k,
+                                   int sync_and_check);
+
 /* ------------------------------------------------------------------------------------------ */
 /* the 16x16x16 unit: one WMMA multiply-accumulate                                             */
 /* ------------------------------------------------------------------------------------------ */
