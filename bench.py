@@ -204,12 +204,13 @@ def run_ours(args):
 
     sharded = name == "sharded"
     if sharded:
-        sg = ShardedGemm(h, M, N, K, panels=args.panels, reserve_ctas=args.nccl_ctas)
+        sg = ShardedGemm(h, M, N, K, panels=args.panels, transport=args.transport,
+                         reserve_ctas=args.nccl_ctas if args.transport == "nccl" else args.fence_ctas)
         n0, ns = sg.n0, sg.slab_cols
     else:
         sg, n0, ns = None, 0, N
     a_rows, a_cols = (K, M) if w["transA"] else (M, K)
-    A = torch.empty(a_rows * a_cols, dtype=torch.float16, device="cuda")
+    A = sg.alloc_a() if sharded else torch.empty(a_rows * a_cols, dtype=torch.float16, device="cuda")
     B = torch.empty(K * max(ns, 1), dtype=torch.float16, device="cuda")
     Cm = torch.empty(M * max(ns, 1), dtype=torch.float32, device="cuda") if w["beta"] != 0.0 else None
     D = torch.empty(M * max(ns, 1), dtype=torch.float32, device="cuda")
@@ -323,6 +324,9 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = float(t.item())
     e2e_tflops = flops / e2e_s / 1e12
+    if sharded:
+        barrier()
+        sg.close()
 
     if rank != 0:
         if dist is not None:
@@ -349,7 +353,7 @@ def run_ours(args):
         "config": {"workload": name, "M": M, "N": N, "K": K, "transA": w["transA"], "transB": w["transB"],
                    "alpha": w["alpha"], "beta": w["beta"], "seed": w["seed"],
                    "l2": f"inputs+outputs {algorithmic_bytes(w) / 1e6:.0f} MB per step exceed the 126 MB L2; no flush",
-                   "kernel": launch, "parallelism": f"N-sharded x{world}, A broadcast (NCCL) in {len(sg.panels)} K-panels" if sharded else "1 GPU"},
+                   "kernel": launch, "parallelism": (f"N-sharded x{world}, A sent in {len(sg.panels)} K-panels by " + ("NCCL broadcast" if sg.transport == "nccl" else "copy-engine scatter + all-gather over NVLink, NCCL fences")) if sharded else "1 GPU"},
         "clocks": clocks,
         "e2e": {"value": round(e2e_tflops, 3), "unit": "TFLOP/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
                 "steps": e2e_steps, "api": "ShardedGemm.run + pinned copies" if sharded else "b200_gemm_f16f32_host"},
@@ -419,7 +423,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
     ap.add_argument("--panels", type=int, default=8, help="K panels of the A broadcast (sharded)")
-    ap.add_argument("--nccl-ctas", type=int, default=8, help="SMs left to NCCL while a broadcast is in flight")
+    ap.add_argument("--nccl-ctas", type=int, default=8, help="SMs left to NCCL while a broadcast is in flight (transport nccl)")
+    ap.add_argument("--fence-ctas", type=int, default=4, help="SMs left free for the fence all-reduces (transport p2p)")
+    ap.add_argument("--transport", default="p2p", choices=["p2p", "nccl"], help="how A reaches the other ranks (sharded)")
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()

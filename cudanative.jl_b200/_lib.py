@@ -52,6 +52,10 @@ SIGNATURES = {
     "b200_host_free": (_i, [_p]),
     "b200_memcpy_h2d": (_i, [_p, _p, _sz, _p]),
     "b200_memcpy_d2h": (_i, [_p, _p, _sz, _p]),
+    "b200_ipc_get_handle": (_i, [_p, _p]),
+    "b200_ipc_open_handle": (_i, [_p, _pp]),
+    "b200_ipc_close_handle": (_i, [_p]),
+    "b200_memcpy_d2d": (_i, [_p, _p, _sz, _p]),
     "b200_memset": (_i, [_p, _i, _sz, _p]),
     "b200_stream_sync": (_i, [_p]),
     "b200_fill_f16": (_i, [_p, _p, _i64, _i64, _i64, _u64, _u64, _u64, _i, _f]),

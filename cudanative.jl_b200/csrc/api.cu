@@ -424,6 +424,31 @@ int b200_memcpy_d2h(void* dst, const void* src, size_t bytes, b200_stream stream
     B200_CUDA_TRY(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)));
     return B200_OK;
 }
+int b200_ipc_get_handle(void* dptr, void* handle64) {
+    if (!dptr || !handle64) return fail(B200_INVALID_ARG, "ipc_get_handle: null argument");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "CUDA IPC handles are 64 bytes");
+    cudaIpcMemHandle_t hnd;
+    B200_CUDA_TRY(cudaIpcGetMemHandle(&hnd, dptr));
+    std::memcpy(handle64, &hnd, sizeof(hnd));
+    return B200_OK;
+}
+int b200_ipc_open_handle(const void* handle64, void** dptr) {
+    if (!dptr || !handle64) return fail(B200_INVALID_ARG, "ipc_open_handle: null argument");
+    *dptr = nullptr;
+    cudaIpcMemHandle_t hnd;
+    std::memcpy(&hnd, handle64, sizeof(hnd));
+    B200_CUDA_TRY(cudaIpcOpenMemHandle(dptr, hnd, cudaIpcMemLazyEnablePeerAccess));
+    return B200_OK;
+}
+int b200_ipc_close_handle(void* dptr) {
+    if (dptr) B200_CUDA_TRY(cudaIpcCloseMemHandle(dptr));
+    return B200_OK;
+}
+int b200_memcpy_d2d(void* dst, const void* src, size_t bytes, b200_stream stream) {
+    if (bytes && (!dst || !src)) return fail(B200_INVALID_ARG, "memcpy_d2d: null pointer");
+    B200_CUDA_TRY(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault, static_cast<cudaStream_t>(stream)));
+    return B200_OK;
+}
 int b200_memset(void* dst, int byte, size_t bytes, b200_stream stream) {
     B200_CUDA_TRY(cudaMemsetAsync(dst, byte, bytes, static_cast<cudaStream_t>(stream)));
     return B200_OK;

@@ -216,6 +216,18 @@ int b200_memcpy_d2h(void* dst, const void* src, size_t bytes, b200_stream stream
 int b200_memset(void* dst, int byte, size_t bytes, b200_stream stream);
 int b200_stream_sync(b200_stream stream);
 
+/* Peer access for the N-sharded multi-GPU GEMM, one process per GPU (no counterpart in the
+ * reference, whose only multi-device facility is picking a device per task: src/init.jl:187-209).
+ * b200_ipc_get_handle writes the 64-byte CUDA IPC handle of a b200_malloc'ed buffer;
+ * b200_ipc_open_handle maps another process's buffer into this one (peer access is enabled on
+ * demand) and b200_ipc_close_handle unmaps it.  b200_memcpy_d2d copies between any two device
+ * addresses, local or mapped, on a stream; between GPUs it runs on the copy engines over NVLink
+ * and takes no SM away from a GEMM that is running. */
+int b200_ipc_get_handle(void* dptr, void* handle64);
+int b200_ipc_open_handle(const void* handle64, void** dptr);
+int b200_ipc_close_handle(void* dptr);
+int b200_memcpy_d2d(void* dst, const void* src, size_t bytes, b200_stream stream);
+
 /* Counter-based synthetic matrices (no counterpart in the reference, whose tests draw from
  * Julia's unseeded rand; test/device/wmma.jl:196-199).  Element (i, j) of a rows x cols
  * column-major matrix gets

@@ -57,6 +57,7 @@ def main():
     backend = sys.argv[1]
     M, N, K = (int(x) for x in sys.argv[2:5])
     panels = int(sys.argv[5]) if len(sys.argv) > 5 else 4
+    transport = sys.argv[6] if len(sys.argv) > 6 else "nccl"
     seed, alpha, beta = 4, 1.0, 1.0
     rank = int(os.environ["RANK"])
     if backend == "nccl":
@@ -73,13 +74,19 @@ def main():
         dist.init_process_group("gloo")
         handle = OracleHandle()
         dev = torch.device("cpu")
-    sg = ShardedGemm(handle, M, N, K, panels=panels, reserve_ctas=8, sm_count=148)
+    sg = ShardedGemm(handle, M, N, K, panels=panels, reserve_ctas=8, sm_count=148, transport=transport)
     n0, ns = sg.n0, sg.slab_cols
     a_host = rng.matrix(seed, 0, M, K, rng.NORMAL, K ** -0.5, np.float16)
     b_host = rng.window(seed, 1, K, 0, K, n0, n0 + ns, rng.NORMAL, K ** -0.5, np.float16)
     c_host = rng.window(seed, 2, M, 0, M, n0, n0 + ns, rng.NORMAL, 1.0, np.float32)
     # torch holds the column-major matrices as their transposes
-    A = torch.from_numpy(np.ascontiguousarray(a_host.T)).to(dev) if rank == 0 else torch.zeros((K, M), dtype=torch.float16, device=dev)
+    if backend == "nccl":
+        A = sg.alloc_a()
+        A.zero_()
+        if rank == 0:
+            A.copy_(torch.from_numpy(np.ascontiguousarray(a_host.T)).reshape(-1))
+    else:
+        A = torch.from_numpy(np.ascontiguousarray(a_host.T)).to(dev) if rank == 0 else torch.zeros((K, M), dtype=torch.float16, device=dev)
     B = torch.from_numpy(np.ascontiguousarray(b_host.T)).to(dev) if ns else torch.zeros((1,), dtype=torch.float16, device=dev)
     Cm = torch.from_numpy(np.ascontiguousarray(c_host.T)).to(dev) if ns else torch.zeros((1,), dtype=torch.float32, device=dev)
     D = torch.full((max(ns, 1), M), -3.0, dtype=torch.float32, device=dev)
@@ -90,7 +97,7 @@ def main():
             code, block, _ = handle.device_status()
             assert code == 0, f"rank {rank}: device wait {code} ran out in block {block}"
     if rank != 0:
-        assert np.array_equal(A.cpu().numpy().T, a_host), f"rank {rank}: A was not broadcast intact"
+        assert np.array_equal(A.cpu().numpy().reshape(K, M).T, a_host), f"rank {rank}: A did not arrive intact"
     if ns:
         d = D.cpu().numpy().T
         oracle.assert_close(d, oracle.gemm_ref(False, False, alpha, a_host, b_host, beta, c_host), f"rank {rank} slab [{n0},{n0 + ns})")
@@ -101,6 +108,9 @@ def main():
         caps = [c for (_, c) in handle.calls[:len(want)]]
         assert all(c == 140 for c in caps[:-1]) and caps[-1] == 0, caps  # SMs left to NCCL except on the last panel
     dist.barrier()
+    if backend == "nccl":
+        torch.cuda.synchronize()
+        sg.close()
     dist.destroy_process_group()
     print(f"rank {rank} ok: slab [{n0},{n0 + ns}) of N={N}, {len(sg.panels)} panels", flush=True)
 
