@@ -204,8 +204,8 @@ def run_ours(args):
 
     sharded = name == "sharded"
     if sharded:
-        sg = ShardedGemm(h, M, N, K, panels=args.panels, transport=args.transport,
-                         reserve_ctas=args.nccl_ctas if args.transport == "nccl" else args.fence_ctas)
+        sg = ShardedGemm(h, M, N, K, panels=args.panels, transport=args.transport, fused=args.gated,
+                         reserve_ctas=args.nccl_ctas if args.transport == "nccl" else 0)
         n0, ns = sg.n0, sg.slab_cols
     else:
         sg, n0, ns = None, 0, N
@@ -332,7 +332,7 @@ def run_ours(args):
         if dist is not None:
             dist.destroy_process_group()
         return
-    launches_per_step = (len(sg.panels) if sharded else 1) * (2 if launch["split_k"] > 1 else 1)
+    launches_per_step = ((1 if sg.fused else len(sg.groups)) if sharded else 1) * (2 if launch["split_k"] > 1 else 1)
     hbm_bound = name == "skinny"
     # kernel-level roofline: one launch == one step for the single-GPU workloads
     if hbm_bound:
@@ -353,7 +353,7 @@ def run_ours(args):
         "config": {"workload": name, "M": M, "N": N, "K": K, "transA": w["transA"], "transB": w["transB"],
                    "alpha": w["alpha"], "beta": w["beta"], "seed": w["seed"],
                    "l2": f"inputs+outputs {algorithmic_bytes(w) / 1e6:.0f} MB per step exceed the 126 MB L2; no flush",
-                   "kernel": launch, "parallelism": (f"N-sharded x{world}, A sent in {len(sg.panels)} K-panels by " + ("NCCL broadcast" if sg.transport == "nccl" else "copy-engine scatter + all-gather over NVLink, NCCL fences")) if sharded else "1 GPU"},
+                   "kernel": launch, "parallelism": (f"N-sharded x{world}, A sent in {len(sg.panels)} K-panels by " + ("NCCL broadcast" if sg.transport == "nccl" else "copy-engine scatter + all-gather over NVLink ordered by stream memory operations" + (", one gated GEMM launch" if sg.fused else f", {len(sg.groups)} GEMM launches over growing K ranges"))) if sharded else "1 GPU"},
         "clocks": clocks,
         "e2e": {"value": round(e2e_tflops, 3), "unit": "TFLOP/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
                 "steps": e2e_steps, "api": "ShardedGemm.run + pinned copies" if sharded else "b200_gemm_f16f32_host"},
@@ -422,9 +422,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
-    ap.add_argument("--panels", type=int, default=8, help="K panels of the A broadcast (sharded)")
+    ap.add_argument("--panels", type=int, default=16, help="K panels in which A travels (sharded)")
     ap.add_argument("--nccl-ctas", type=int, default=8, help="SMs left to NCCL while a broadcast is in flight (transport nccl)")
-    ap.add_argument("--fence-ctas", type=int, default=4, help="SMs left free for the fence all-reduces (transport p2p)")
+    ap.add_argument("--gated", action="store_true", help="p2p transport: one gated GEMM launch instead of a few launches over growing K ranges")
     ap.add_argument("--transport", default="p2p", choices=["p2p", "nccl"], help="how A reaches the other ranks (sharded)")
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")

@@ -38,6 +38,9 @@ SIGNATURES = {
     "b200_selftest_bounded_wait": (_i, [_p, _p, _i64]),
     "b200_last_launch": (_i, [_p, _ip, _ip, _ip, _ip, _ip]),
     "b200_gemm_f16f32": (_i, [_p, _p, _i, _i, _i64, _i64, _i64, _f, _p, _i64, _p, _i64, _f, _p, _i64, _p, _i64]),
+    "b200_gemm_f16f32_gated": (_i, [_p, _p, _i, _i, _i64, _i64, _i64, _f, _p, _i64, _p, _i64, _f, _p, _i64, _p, _i64, _p, _i64]),
+    "b200_stream_write_u32": (_i, [_p, _p, C.c_uint32]),
+    "b200_stream_wait_u32": (_i, [_p, _p, C.c_uint32]),
     "b200_gemm_f16f32_host": (_i, [_p, _i, _i, _i64, _i64, _i64, _f, _p, _i64, _p, _i64, _f, _p, _i64, _p, _i64]),
     "b200_gemm_f16f32_splitk_static": (_i, [_p, _i, _i, _i64, _i64, _i64, _f, _p, _i64, _p, _i64, _f, _p, _i64, _p, _i64, _i, _i]),
     "b200_wmma_16x16x16": (_i, [_p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _f, _p, _i64, _p, _i64, _p, _i64, _p, _i64]),
@@ -58,6 +61,8 @@ SIGNATURES = {
     "b200_memcpy_d2d": (_i, [_p, _p, _sz, _p]),
     "b200_memset": (_i, [_p, _i, _sz, _p]),
     "b200_stream_sync": (_i, [_p]),
+    "b200_stream_create": (_i, [_pp]),
+    "b200_stream_destroy": (_i, [_p]),
     "b200_fill_f16": (_i, [_p, _p, _i64, _i64, _i64, _u64, _u64, _u64, _i, _f]),
     "b200_fill_f32": (_i, [_p, _p, _i64, _i64, _i64, _u64, _u64, _u64, _i, _f]),
 }

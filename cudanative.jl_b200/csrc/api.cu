@@ -1,4 +1,5 @@
 // C ABI of libb200wmma.so: handle, errors, options, GEMM dispatch, host-buffer path, memory.
+#include <cuda.h>
 #include <cuda_runtime.h>
 
 #include <algorithm>
@@ -313,6 +314,61 @@ int b200_gemm_f16f32(b200_handle* h, b200_stream stream, int transA, int transB,
     return run_gemm(h, static_cast<cudaStream_t>(stream), g);
 }
 
+int b200_gemm_f16f32_gated(b200_handle* h, b200_stream stream, int transA, int transB, int64_t M, int64_t N, int64_t K,
+                           float alpha, const void* A, int64_t lda, const void* B, int64_t ldb, float beta,
+                           const float* C, int64_t ldc, float* D, int64_t ldd, const uint32_t* panel_flags,
+                           int64_t panel_k) {
+    if (!h) return fail(B200_INVALID_ARG, "null handle");
+    if (!panel_flags) return fail(B200_INVALID_ARG, "gated gemm: panel_flags is null");
+    GemmProblem g{transA, transB, M, N, K, alpha, beta, A, lda, B, ldb, C, ldc, D, ldd};
+    g.panel_flags = panel_flags;
+    g.panel_k = panel_k;
+    int rc = validate(g);
+    if (rc) return rc;
+    if (M == 0 || N == 0) return B200_OK;
+    std::string why;
+    if (!gemm_tcgen05_eligible(g, &why)) return fail(B200_UNSUPPORTED, "gated gemm needs the TMA path: " + why);
+    const int saved = h->force_kernel, saved_split = h->split_k;
+    h->force_kernel = B200_KERNEL_TCGEN05;
+    h->split_k = 1;
+    rc = run_gemm(h, static_cast<cudaStream_t>(stream), g);
+    h->force_kernel = saved;
+    h->split_k = saved_split;
+    return rc;
+}
+
+int b200_stream_write_u32(b200_stream stream, void* dptr, uint32_t value) {
+    if (!dptr || (reinterpret_cast<uintptr_t>(dptr) & 3u)) return fail(B200_INVALID_ARG, "stream_write_u32: null or misaligned address");
+    using Fn = CUresult (*)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
+    static Fn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        B200_CUDA_TRY(cudaGetDriverEntryPoint("cuStreamWriteValue32", &p, cudaEnableDefault, &q));
+        if (q != cudaDriverEntryPointSuccess || !p) return fail(B200_CUDA_ERROR, "cuStreamWriteValue32 entry point not found");
+        fn = reinterpret_cast<Fn>(p);
+    }
+    CUresult r = fn(static_cast<CUstream>(stream), reinterpret_cast<CUdeviceptr>(dptr), value, 0);
+    if (r != CUDA_SUCCESS) return fail(B200_CUDA_ERROR, "cuStreamWriteValue32 failed (CUresult " + std::to_string(static_cast<int>(r)) + ")");
+    return B200_OK;
+}
+
+int b200_stream_wait_u32(b200_stream stream, void* dptr, uint32_t value) {
+    if (!dptr || (reinterpret_cast<uintptr_t>(dptr) & 3u)) return fail(B200_INVALID_ARG, "stream_wait_u32: null or misaligned address");
+    using Fn = CUresult (*)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
+    static Fn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        B200_CUDA_TRY(cudaGetDriverEntryPoint("cuStreamWaitValue32", &p, cudaEnableDefault, &q));
+        if (q != cudaDriverEntryPointSuccess || !p) return fail(B200_CUDA_ERROR, "cuStreamWaitValue32 entry point not found");
+        fn = reinterpret_cast<Fn>(p);
+    }
+    CUresult r = fn(static_cast<CUstream>(stream), reinterpret_cast<CUdeviceptr>(dptr), value, CU_STREAM_WAIT_VALUE_GEQ);
+    if (r != CUDA_SUCCESS) return fail(B200_CUDA_ERROR, "cuStreamWaitValue32 failed (CUresult " + std::to_string(static_cast<int>(r)) + ")");
+    return B200_OK;
+}
+
 int b200_gemm_f16f32_host(b200_handle* h, int transA, int transB, int64_t M, int64_t N, int64_t K, float alpha,
                           const void* A, int64_t lda, const void* B, int64_t ldb, float beta, const float* C,
                           int64_t ldc, float* D, int64_t ldd) {
@@ -451,6 +507,17 @@ int b200_memcpy_d2d(void* dst, const void* src, size_t bytes, b200_stream stream
 }
 int b200_memset(void* dst, int byte, size_t bytes, b200_stream stream) {
     B200_CUDA_TRY(cudaMemsetAsync(dst, byte, bytes, static_cast<cudaStream_t>(stream)));
+    return B200_OK;
+}
+int b200_stream_create(b200_stream* out) {
+    if (!out) return fail(B200_INVALID_ARG, "stream_create: null out pointer");
+    cudaStream_t s = nullptr;
+    B200_CUDA_TRY(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+    *out = s;
+    return B200_OK;
+}
+int b200_stream_destroy(b200_stream stream) {
+    if (stream) B200_CUDA_TRY(cudaStreamDestroy(static_cast<cudaStream_t>(stream)));
     return B200_OK;
 }
 int b200_stream_sync(b200_stream stream) {

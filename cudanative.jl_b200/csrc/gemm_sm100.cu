@@ -162,6 +162,12 @@ int gemm_tcgen05_launch(const GemmProblem& g, const GemmPlan& plan, float* scrat
     p.kb_total = q.kb_total;
     p.kb_per_split = q.kb_per_split;
     p.raster_group = plan.raster_group > 0 ? plan.raster_group : 8;
+    if (g.panel_flags) {
+        if (g.panel_k <= 0 || g.panel_k % 64) return fail(B200_INVALID_ARG, "gated gemm: panel_k must be a positive multiple of 64");
+        if ((g.K + g.panel_k - 1) / g.panel_k > 32) return fail(B200_INVALID_ARG, "gated gemm: at most 32 panels");
+        p.panel_flags = g.panel_flags;
+        p.kb_per_panel = static_cast<int>(g.panel_k / 64);
+    }
     p.status = status_word;
     p.wait_budget_ns = plan.wait_budget_ns;
 

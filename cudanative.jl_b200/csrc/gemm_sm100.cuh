@@ -40,6 +40,11 @@ struct GemmParams {
     int raster_group;      // tiles_m per rasterisation group
     int out_n_stride;      // column offset between k-slices in the output map (split_k > 1)
     float alpha, beta;     // epilogue scalars (split_k > 1: 1 and 0)
+    // Gated A: when panel_flags != nullptr, k-blocks [j * kb_per_panel, (j + 1) * kb_per_panel) of A
+    // may be loaded only once panel_flags[j] != 0 (written by a stream memory operation after the
+    // panel has arrived in this GPU's memory).  At most 32 panels.
+    const unsigned int* panel_flags;
+    int kb_per_panel;
     int* status;
     unsigned long long wait_budget_ns;
 };
@@ -163,6 +168,7 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             int s = 0;          // stage of the ring
             uint32_t ph = 0;    // its phase bit
             bool ok = true;
+            uint32_t panels_seen = p.panel_flags ? 0u : 0xffffffffu;  // bit j: panel j is known to be here
 #ifdef B200_PROBE_SKIP_LOADS
             uint32_t issued = 0;
 #endif
@@ -171,6 +177,14 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 unit_decode(unit, m0, n0, kb0, kb1, out_n0);
                 const int nb0 = n0 + static_cast<int>(cta_rank) * Cfg::BN_LOCAL;
                 for (int kb = kb0; kb < kb1; ++kb, s = (s + 1 == STAGES ? 0 : s + 1), ph ^= (s == 0)) {
+                    if (panels_seen != 0xffffffffu) {
+                        const uint32_t panel = static_cast<uint32_t>(kb / p.kb_per_panel);
+                        if (!((panels_seen >> panel) & 1u)) {
+                            ok = flag_wait(p.panel_flags + panel, wc, kWaitPanel);
+                            if (!ok) break;
+                            panels_seen |= 1u << panel;
+                        }
+                    }
                     ok = mbar_wait<false>(empty_bar(s), ph ^ 1u, wc, kWaitEmptyStage);
                     if (!ok) break;
 #ifdef B200_PROBE_SKIP_LOADS

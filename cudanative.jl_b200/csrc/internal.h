@@ -33,6 +33,10 @@ struct GemmProblem {
     int64_t ldc;
     float* D;
     int64_t ldd;
+    // gated A (optional): columns [j * panel_k, (j + 1) * panel_k) of op(A) may be read only once
+    // panel_flags[j] != 0; panel_k is a multiple of 64
+    const unsigned int* panel_flags = nullptr;
+    int64_t panel_k = 0;
 };
 
 struct GemmPlan {

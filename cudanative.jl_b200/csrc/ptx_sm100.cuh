@@ -108,7 +108,8 @@ enum : int {
     kWaitTmemFull = 104,     // epilogue waiting for the accumulator
     kWaitCTile = 105,        // epilogue waiting for its C chunk
     kWaitUnit = 106,         // 16x16x16 unit waiting for its MMA
-    kWaitSelftest = 107      // the bounded-wait self test (nothing ever arrives)
+    kWaitSelftest = 107,     // the bounded-wait self test (nothing ever arrives)
+    kWaitPanel = 108         // producer waiting for a panel of A to arrive in this GPU's memory
 };
 
 // What a kernel needs to give up on a wait cleanly.
@@ -150,6 +151,32 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
             if (*w.abort_flag) return false;
             if (clock64() - t0 > budget_cycles) {
                 report_timeout(w, where, static_cast<int>(parity));
+                return false;
+            }
+        }
+    }
+}
+
+// Bounded wait for a 32-bit word in global memory to become non-zero.  The word is written by a
+// stream memory operation (not by a kernel) once data that a copy engine moved into this GPU's
+// memory is complete; the acquire at system scope plus the proxy fence order the bulk loads that
+// follow after the data.
+__device__ __forceinline__ bool flag_wait(const unsigned int* flag, const WaitCtx& w, int where) {
+    const long long t0 = clock64();
+    const long long budget_cycles = static_cast<long long>(w.budget_ns) * 2;
+    uint32_t spins = 0;
+    for (;;) {
+        unsigned int v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+        if (v != 0u) {
+            asm volatile("fence.proxy.async;" ::: "memory");
+            return true;
+        }
+        __nanosleep(200);
+        if ((++spins & 15u) == 0u) {
+            if (*w.abort_flag) return false;
+            if (clock64() - t0 > budget_cycles) {
+                report_timeout(w, where, static_cast<int>(spins));
                 return false;
             }
         }

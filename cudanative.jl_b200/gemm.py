@@ -76,6 +76,16 @@ class Handle:
         _lib.check(_lib.lib().b200_gemm_f16f32(self._h, stream, int(bool(transA)), int(bool(transB)), M, N, K,
                                                float(alpha), a, lda, b, ldb, float(beta), c, ldc, d, ldd), "gemm")
 
+    def gemm_gated(self, transA: bool, transB: bool, M: int, N: int, K: int, alpha: float, A, lda: int, B, ldb: int,
+                   beta: float, Cm, ldc: int, D, ldd: int, panel_flags, panel_k: int, stream=None) -> None:
+        """``gemm`` whose main loop reads columns [j*panel_k, (j+1)*panel_k) of op(A) only once the
+        32-bit device word ``panel_flags[j]`` is non-zero (b200_gemm_f16f32_gated)."""
+        a, b, d = _addr(A), _addr(B), _addr(D)
+        c = _addr(Cm) if Cm is not None else None
+        _lib.check(_lib.lib().b200_gemm_f16f32_gated(self._h, stream, int(bool(transA)), int(bool(transB)), M, N, K,
+                                                     float(alpha), a, lda, b, ldb, float(beta), c, ldc, d, ldd,
+                                                     _addr(panel_flags), panel_k), "gemm_gated")
+
     # -- host buffers (numpy, ideally page-locked) ---------------------------------------------
     def gemm_host(self, transA: bool, transB: bool, M: int, N: int, K: int, alpha: float, A: np.ndarray, lda: int,
                   B: np.ndarray, ldb: int, beta: float, Cm, ldc: int, D: np.ndarray, ldd: int) -> None:
@@ -167,11 +177,11 @@ class _RawCudaBuffer:
     """A b200_malloc'ed device buffer exposed through ``__cuda_array_interface__`` so that torch can
     view it without copying (the IPC handle of a cudaMalloc'ed block is what peers can map)."""
 
-    def __init__(self, nbytes: int):
+    def __init__(self, nbytes: int, typestr: str = "<f2", itemsize: int = 2):
         p = C.c_void_p()
         _lib.check(_lib.lib().b200_malloc(C.byref(p), nbytes), "b200_malloc")
         self.ptr, self.nbytes = p.value, nbytes
-        self.__cuda_array_interface__ = {"shape": (nbytes // 2,), "typestr": "<f2", "data": (self.ptr, False),
+        self.__cuda_array_interface__ = {"shape": (nbytes // itemsize,), "typestr": typestr, "data": (self.ptr, False),
                                          "version": 2, "strides": None}
 
     def free(self):
@@ -180,28 +190,58 @@ class _RawCudaBuffer:
             self.ptr = None
 
 
+def launch_groups(n_panels: int, first: int = 1, growth: float = 2.5) -> list[tuple[int, int]]:
+    """Group n transfer panels into GEMM launches [p0, p1) of geometrically growing size: the first
+    launch starts as soon as little of A has arrived, later launches are long enough that their
+    fixed cost and their extra pass over D do not matter.  While launch i computes, the panels of
+    launch i+1 arrive: with compute slower than the transfer, growth up to 1 + compute/transfer
+    keeps every launch fed."""
+    out, p, size = [], 0, float(max(1, first))
+    while p < n_panels:
+        q = min(n_panels, p + max(1, int(round(size))))
+        out.append((p, q))
+        size *= growth
+        p = q
+    if len(out) > 1 and out[-1][1] - out[-1][0] < (out[-2][1] - out[-2][0]) // 2:
+        last = out.pop()
+        out[-1] = (out[-1][0], last[1])
+    return out
+
+
 class ShardedGemm:
     """``D[:, slab_r] = alpha * A * B[:, slab_r] + beta * C[:, slab_r]`` on every rank r.
 
     One process per GPU.  B, C and D are split into contiguous column slabs that never move; A
-    (M x K column-major, lda = M) starts on rank 0 and reaches every rank in K panels.  Panel p's
-    GEMM (accumulating into D) runs while later panels are still in flight, so only the first
-    panel's transfer is exposed.  There is no output collective: D stays sharded like C.
+    (M x K column-major, lda = M) starts on rank 0 and reaches every rank in K panels, while the
+    GEMM on the panels that have already arrived is running.  There is no output collective: D
+    stays sharded like C.
 
     Two transports for A:
 
     ``"nccl"``  ``broadcast(panel, src=0)`` per panel through torch.distributed (NCCL on GPUs, gloo in
                 the CPU tests).  NCCL's broadcast is an SM kernel: the persistent GEMM grid leaves
                 ``reserve_ctas`` SMs to it, and its bandwidth follows the CTAs it is given.
-    ``"p2p"``   copy engines over NVLink, no SMs: per panel, rank 0 sends sub-block g of the panel to
-                rank g, then every rank sends its sub-block to all others (a scatter followed by an
-                all-gather, so no GPU sends more than the panel's size), each step fenced by a
-                4-byte NCCL all-reduce that every rank enqueues behind its own copies.  Needs A in
-                a buffer from ``alloc_a()`` (peers map it through CUDA IPC).
+    ``"p2p"``   copy engines over NVLink, no SMs and no kernels at all: per panel, rank 0 copies
+                sub-block g of the panel into rank g's A (scatter), then every rank copies its
+                sub-block into every other rank's A (all-gather), so no GPU sends more than the
+                panel's size.  Arrival is signalled by stream memory operations: behind each copy the
+                sender's stream writes the call's epoch into a flag word in the receiver's memory,
+                and the receiver's streams wait for that word before they forward the data or launch
+                the GEMM that reads it.  Needs A in the buffer from ``alloc_a()`` (peers map it and
+                the flag words through CUDA IPC).
+
+    The product itself is a sequence of GEMM launches over growing K ranges (``launch_groups``), each
+    accumulating into D and ordered behind the arrival of its own panels only; with ``fused=True``
+    (p2p) it is instead ONE launch of the gated GEMM, whose TMA producer waits for per-panel flag
+    words itself -- that form overlaps transfer and main loop inside one kernel and writes D once,
+    but its first wave of tiles cannot finish before all of A has arrived.
     """
 
-    def __init__(self, handle: Handle, M: int, N: int, K: int, *, panels: int = 8, reserve_ctas: int | None = None,
-                 group=None, sm_count: int | None = None, transport: str = "nccl"):
+    MAX_PANELS = 32
+
+    def __init__(self, handle: Handle, M: int, N: int, K: int, *, panels: int = 16, reserve_ctas: int | None = None,
+                 group=None, sm_count: int | None = None, transport: str = "nccl", fused: bool = False,
+                 grouping: str | None = None):
         import torch
         import torch.distributed as dist
 
@@ -214,143 +254,232 @@ class ShardedGemm:
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.transport = transport if self.world > 1 else "nccl"
+        self.fused = bool(fused) and self.world > 1
+        if self.fused and self.transport != "p2p":
+            raise ValueError("fused=True needs the p2p transport")
         self.n0, self.n1 = slab_bounds(N, self.world, self.rank)
-        self.panels = panel_bounds(K, panels if self.world > 1 else 1)
+        # transfer panels: equal ranges of whole 64-wide k-blocks
+        panels = max(1, min(panels if self.world > 1 else 1, self.MAX_PANELS))
+        self.panel_k = -(-(-(-K // panels)) // 64) * 64  # ceil(ceil(K / panels) / 64) * 64
+        self.panels = [(k0, min(K, k0 + self.panel_k)) for k0 in range(0, K, self.panel_k)]
+        # GEMM launches: groups of consecutive panels
+        if grouping is None:
+            grouping = "geometric" if self.transport == "p2p" else "each"
+        if grouping == "geometric":
+            self.groups = launch_groups(len(self.panels))
+        elif grouping == "each":
+            self.groups = [(p, p + 1) for p in range(len(self.panels))]
+        else:
+            raise ValueError("grouping must be 'geometric' or 'each'")
         if reserve_ctas is None:
-            reserve_ctas = 4 if self.transport == "p2p" else 8
+            reserve_ctas = 0 if self.transport == "p2p" else 8
         self.reserve_ctas = reserve_ctas if self.world > 1 else 0
         if sm_count is None:
             sm_count = torch.cuda.get_device_properties(handle.device).multi_processor_count
         self.sm_count = sm_count
         self._raw = None
+        self._raw_flags = None
         self._peers = {}
-        self._copy_stream = None
-        self._flag = None
+        self._peer_flags = {}
+        self._scatter_stream = None
+        self._gather_stream = None
+        self._gate_words = None
+        self._epoch = 0
         self.A = None
 
     @property
     def slab_cols(self) -> int:
         return self.n1 - self.n0
 
+    # flag words (uint32 each) in every rank's flag buffer
+    def _w_done(self, g):      # rank g has finished everything that touched A in the previous call
+        return 4 * g
+    def _w_scat(self, p):      # my sub-block of panel p has arrived from rank 0
+        return 4 * (64 + p)
+    def _w_gath(self, p, g):   # rank g's sub-block of panel p has arrived
+        return 4 * (128 + p * 64 + g)
+    _FLAG_BYTES = 4 * (128 + 32 * 64)
+
     # ------------------------------------------------------------------------------------------
     def alloc_a(self):
         """The M*K float16 buffer that holds A on this rank (flat torch tensor, column-major data).
-        With the p2p transport it is a cudaMalloc'ed block whose IPC handle every peer maps."""
+        With the p2p transport it is a cudaMalloc'ed block which, like the block of flag words
+        beside it, every peer maps through CUDA IPC."""
         torch, dist = self.torch, self.dist
         if self.A is not None:
             return self.A
         n = self.M * self.K
+        dev = torch.device("cuda", self.handle.device)
         if self.transport != "p2p":
-            self.A = torch.empty(n, dtype=torch.float16, device=torch.device("cuda", self.handle.device))
+            self.A = torch.empty(n, dtype=torch.float16, device=dev)
             return self.A
+        if self.world > 64:
+            raise ValueError("the p2p transport supports at most 64 ranks")
         L = _lib.lib()
         self._raw = _RawCudaBuffer(2 * n)
-        self.A = torch.as_tensor(self._raw, device=torch.device("cuda", self.handle.device))
-        hnd = C.create_string_buffer(64)
-        _lib.check(L.b200_ipc_get_handle(self._raw.ptr, hnd), "ipc_get_handle")
+        self._raw_flags = _RawCudaBuffer(self._FLAG_BYTES)
+        _lib.check(L.b200_memset(self._raw_flags.ptr, 0, self._FLAG_BYTES, None), "clear flags")
+        _lib.check(L.b200_stream_sync(None), "clear flags")
+        self.A = torch.as_tensor(self._raw, device=dev)
+        mine = []
+        for buf in (self._raw, self._raw_flags):
+            hnd = C.create_string_buffer(64)
+            _lib.check(L.b200_ipc_get_handle(buf.ptr, hnd), "ipc_get_handle")
+            mine.append(bytes(hnd.raw))
         handles = [None] * self.world
-        dist.all_gather_object(handles, bytes(hnd.raw), group=self.group)
-        for g, raw in enumerate(handles):
+        dist.all_gather_object(handles, mine, group=self.group)  # also orders the clears above before any use
+        for g, (ha, hf) in enumerate(handles):
             if g == self.rank:
                 continue
-            p = C.c_void_p()
-            _lib.check(L.b200_ipc_open_handle(raw, C.byref(p)), f"ipc_open_handle(rank {g})")
-            self._peers[g] = p.value
-        self._copy_stream = torch.cuda.Stream()
-        self._flag = torch.ones(1, dtype=torch.int32, device=self.A.device)
+            pa, pf = C.c_void_p(), C.c_void_p()
+            _lib.check(L.b200_ipc_open_handle(ha, C.byref(pa)), f"ipc_open_handle(A of rank {g})")
+            _lib.check(L.b200_ipc_open_handle(hf, C.byref(pf)), f"ipc_open_handle(flags of rank {g})")
+            self._peers[g], self._peer_flags[g] = pa.value, pf.value
+        self._scatter_stream = torch.cuda.Stream()
+        self._gather_stream = torch.cuda.Stream()
+        self._gate_words = torch.zeros(self.MAX_PANELS, dtype=torch.int32, device=dev)
         return self.A
 
     def close(self) -> None:
-        """Unmap the peers' buffers and free this rank's A (p2p transport).  Collective in spirit:
-        call it on every rank, after the last product has been synchronised."""
+        """Unmap the peers' buffers and free this rank's A and flags (p2p transport).  Call it on
+        every rank after the last product has been synchronised everywhere."""
         L = _lib.lib()
-        for p in self._peers.values():
+        for p in list(self._peers.values()) + list(self._peer_flags.values()):
             L.b200_ipc_close_handle(p)
-        self._peers = {}
+        self._peers, self._peer_flags = {}, {}
         self.A = None
-        if self._raw is not None:
-            self._raw.free()
-            self._raw = None
+        for buf in (self._raw, self._raw_flags):
+            if buf is not None:
+                buf.free()
+        self._raw = self._raw_flags = None
 
     # ------------------------------------------------------------------------------------------
-    def _fence(self):
-        """4-byte all-reduce enqueued behind everything on the current stream; its completion on a
-        rank means every rank got that far.  Returns the async work handle."""
-        return self.dist.all_reduce(self._flag, op=self.dist.ReduceOp.MAX, group=self.group, async_op=True)
-
-    def _send_panels_p2p(self, a_addr: int):
-        """Enqueue the scatter + all-gather of every K panel on the copy stream; returns one work
-        handle per panel whose completion means the panel is complete on every rank."""
+    def _send_panels_p2p(self, a_addr: int, cur_stream: int) -> int:
+        """Enqueue the scatter + all-gather of every K panel on the two transfer streams and the
+        flag writes that announce them.  Returns the epoch the flag words will carry."""
         torch, L = self.torch, _lib.lib()
         M, G, r = self.M, self.world, self.rank
-        cs = self._copy_stream
-        cs.wait_stream(torch.cuda.current_stream())  # what the caller enqueued so far comes first
-        ready = []
-        with torch.cuda.stream(cs):
-            self._fence().wait()  # nobody still reads or fills the A of the previous call
-            for (k0, k1) in self.panels:
-                sub = [(k0 + c0, k0 + c1) for (c0, c1) in (slab_bounds(k1 - k0, G, g, align=8) for g in range(G))]
-                if r == 0:  # scatter: sub-block g goes to rank g
-                    for g in range(1, G):
-                        c0, c1 = sub[g]
-                        if c1 > c0:
-                            _lib.check(L.b200_memcpy_d2d(self._peers[g] + 2 * c0 * M, a_addr + 2 * c0 * M,
-                                                         2 * (c1 - c0) * M, cs.cuda_stream), "scatter copy")
-                self._fence().wait()
-                c0, c1 = sub[r]  # all-gather: my sub-block goes to everybody but rank 0, which has it all
-                if c1 > c0:
-                    for h in range(1, G):
-                        if h != r:
-                            _lib.check(L.b200_memcpy_d2d(self._peers[h] + 2 * c0 * M, a_addr + 2 * c0 * M,
-                                                         2 * (c1 - c0) * M, cs.cuda_stream), "all-gather copy")
-                ready.append(self._fence())
-        return ready
+        s1, s2 = self._scatter_stream, self._gather_stream
+        flags = self._raw_flags.ptr
+        self._epoch += 1
+        e = self._epoch
+
+        def write(stream, addr):
+            _lib.check(L.b200_stream_write_u32(stream, addr, e), "flag write")
+
+        def wait(stream, addr):
+            _lib.check(L.b200_stream_wait_u32(stream, addr, e), "flag wait")
+
+        def copy(stream, dst_rank, c0, c1):
+            _lib.check(L.b200_memcpy_d2d(self._peers[dst_rank] + 2 * c0 * M, a_addr + 2 * c0 * M, 2 * (c1 - c0) * M,
+                                         stream), "panel copy")
+
+        # Everything the caller enqueued so far (the previous product reading A, a refill of A on
+        # rank 0) precedes "I am done with my A": tell every peer, then wait until every peer says so.
+        for g in range(G):
+            if g != r:
+                write(cur_stream, self._peer_flags[g] + self._w_done(r))
+        cur = torch.cuda.current_stream()
+        s1.wait_stream(cur)
+        s2.wait_stream(cur)
+        for st in ((s1, s2) if r == 0 else (s2,)):
+            for g in range(G):
+                if g != r:
+                    wait(st.cuda_stream, flags + self._w_done(g))
+        if self.fused:  # re-arm the gates of the one-launch form
+            _lib.check(L.b200_memset(self._gate_words.data_ptr(), 0, 4 * self.MAX_PANELS, cur_stream), "reset gates")
+            s2.wait_stream(cur)
+        for p, (k0, k1) in enumerate(self.panels):
+            sub = [(k0 + c0, k0 + c1) for (c0, c1) in (slab_bounds(k1 - k0, G, g, align=8) for g in range(G))]
+            if r == 0:  # scatter: sub-block g goes to rank g
+                for g in range(1, G):
+                    c0, c1 = sub[g]
+                    if c1 > c0:
+                        copy(s1.cuda_stream, g, c0, c1)
+                    write(s1.cuda_stream, self._peer_flags[g] + self._w_scat(p))
+            else:
+                wait(s2.cuda_stream, flags + self._w_scat(p))
+            c0, c1 = sub[r]  # all-gather: my sub-block goes to everybody but rank 0, which has it all
+            for h in range(1, G):
+                if h != r:
+                    if c1 > c0:
+                        copy(s2.cuda_stream, h, c0, c1)
+                    write(s2.cuda_stream, self._peer_flags[h] + self._w_gath(p, r))
+            if self.fused and r != 0:
+                for g in range(G):
+                    if g != r:
+                        wait(s2.cuda_stream, flags + self._w_gath(p, g))
+                write_gate = self._gate_words.data_ptr() + 4 * p
+                _lib.check(L.b200_stream_write_u32(s2.cuda_stream, write_gate, 1), "open panel gate")
+        return e
+
+    def _wait_panels(self, stream: int, p0: int, p1: int, e: int) -> None:
+        """Order `stream` behind the arrival of panels [p0, p1) on this rank."""
+        if self.rank == 0:
+            return  # rank 0 holds all of A from the start
+        L, flags = _lib.lib(), self._raw_flags.ptr
+        for p in range(p0, p1):
+            _lib.check(L.b200_stream_wait_u32(stream, flags + self._w_scat(p), e), "flag wait")
+            for g in range(self.world):
+                if g != self.rank:
+                    _lib.check(L.b200_stream_wait_u32(stream, flags + self._w_gath(p, g), e), "flag wait")
 
     def run(self, alpha: float, A, B_slab, beta: float, C_slab, D_slab, stream=None) -> None:
         """A: device buffer of M*K float16 on every rank (contents valid on rank 0 only before the
         call, on every rank after it; with the p2p transport it must be ``alloc_a()``'s buffer).
         B_slab: K x slab_cols (ldb = K).  C_slab / D_slab: M x slab_cols (ld = M).  All column-major
-        torch tensors (flat or 2-D, any shape with the right number of elements)."""
+        torch tensors (flat or 2-D, any shape with the right number of elements).  Every rank must
+        make the call, also one whose slab is empty."""
         torch, dist = self.torch, self.dist
         M, K, ns = self.M, self.K, self.slab_cols
         a_flat = A.view(-1)
         a_addr = a_flat.data_ptr()
-        works = []
-        if self.world > 1:
-            if self.transport == "p2p":
-                if self._raw is None or a_addr != self._raw.ptr:
-                    raise ValueError("the p2p transport needs A in the buffer returned by alloc_a()")
-                works = self._send_panels_p2p(a_addr)
-            else:
-                for (k0, k1) in self.panels:
-                    view = a_flat[k0 * M:k1 * M]
-                    works.append(dist.broadcast(view, src=dist.get_global_rank(self.group, 0) if self.group else 0,
-                                                group=self.group, async_op=True))
-        if ns == 0:
-            for w in works:
-                w.wait()
-            return
+        if stream is not None:
+            s = stream
+        else:
+            s = torch.cuda.current_stream().cuda_stream if a_flat.is_cuda else None
+        works, epoch = [], 0
+        p2p = self.world > 1 and self.transport == "p2p"
+        if p2p:
+            if self._raw is None or a_addr != self._raw.ptr:
+                raise ValueError("the p2p transport needs A in the buffer returned by alloc_a()")
+            epoch = self._send_panels_p2p(a_addr, s)
+        elif self.world > 1:
+            for (k0, k1) in self.panels:
+                view = a_flat[k0 * M:k1 * M]
+                works.append(dist.broadcast(view, src=dist.get_global_rank(self.group, 0) if self.group else 0,
+                                            group=self.group, async_op=True))
         h = self.handle
         saved = h.get_option(_lib.OPT_MAX_CTAS)
         b_addr = B_slab.data_ptr()
         c_addr = C_slab.data_ptr() if C_slab is not None else None
         d_addr = D_slab.data_ptr()
-        if stream is not None:
-            s = stream
-        else:
-            s = torch.cuda.current_stream().cuda_stream if a_flat.is_cuda else None
+        reserved = max(2, (self.sm_count - self.reserve_ctas) // 2 * 2) if self.reserve_ctas else saved
         try:
-            for p, (k0, k1) in enumerate(self.panels):
-                last = p == len(self.panels) - 1
-                if works:
-                    works[p].wait()  # stream-level: the GEMM below is ordered after panel p
-                if self.reserve_ctas and not last:
-                    # transfers (or their fences) are still in flight: leave them a few SMs
-                    h.set_option(_lib.OPT_MAX_CTAS, max(2, (self.sm_count - self.reserve_ctas) // 2 * 2))
+            if self.fused and p2p:
+                if ns:
+                    # one launch: the producer warps wait for the panel gates themselves
+                    h.set_option(_lib.OPT_MAX_CTAS, reserved)
+                    if self.rank == 0:  # rank 0 has all of A: open every gate at once
+                        _lib.check(_lib.lib().b200_memset(self._gate_words.data_ptr(), 1, 4 * self.MAX_PANELS, s), "open gates")
+                    h.gemm_gated(False, False, M, ns, K, alpha, a_addr, M, b_addr, K, beta, c_addr, M, d_addr, M,
+                                 self._gate_words.data_ptr(), self.panel_k, stream=s)
+                self._wait_panels(s, 0, len(self.panels), epoch)  # later work on this stream sees all of A
+                return
+            for i, (p0, p1) in enumerate(self.groups):
+                last = i == len(self.groups) - 1
+                if p2p:
+                    self._wait_panels(s, p0, p1, epoch)
                 else:
-                    h.set_option(_lib.OPT_MAX_CTAS, saved)
+                    for w in works[p0:p1]:
+                        w.wait()  # stream-level: the GEMM below is ordered after these panels
+                if not ns:
+                    continue
+                # while transfers that need SMs are still in flight, leave them a few
+                h.set_option(_lib.OPT_MAX_CTAS, saved if last else reserved)
+                k0, k1 = self.panels[p0][0], self.panels[p1 - 1][1]
                 h.gemm(False, False, M, ns, k1 - k0, alpha, a_addr + 2 * k0 * M, M, b_addr + 2 * k0, K,
-                       beta if p == 0 else 1.0, c_addr if p == 0 else d_addr, M, d_addr, M, stream=s)
+                       beta if i == 0 else 1.0, c_addr if i == 0 else d_addr, M, d_addr, M, stream=s)
         finally:
             h.set_option(_lib.OPT_MAX_CTAS, saved)
 

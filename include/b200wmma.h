@@ -133,6 +133,28 @@ int b200_gemm_f16f32(b200_handle* h, b200_stream stream, int transA, int transB,
                      int64_t N, int64_t K, float alpha, const void* A, int64_t lda, const void* B,
                      int64_t ldb, float beta, const float* C, int64_t ldc, float* D, int64_t ldd);
 
+/* b200_gemm_f16f32 whose main loop may start before all of A is in this GPU's memory: columns
+ * [j*panel_k, (j+1)*panel_k) of op(A) are read only once the 32-bit word panel_flags[j] (device
+ * memory) is non-zero.  panel_k is a multiple of 64; at most 32 panels.  The words are meant to
+ * be written with b200_stream_write_u32 on the stream that moves A (behind the copy of that
+ * panel), so that one GEMM launch overlaps the arrival of A over NVLink.  A wait for a panel is
+ * bounded like every other wait (wait id 108).  No counterpart in the reference (single GPU
+ * only, src/init.jl:187-209). */
+int b200_gemm_f16f32_gated(b200_handle* h, b200_stream stream, int transA, int transB, int64_t M,
+                           int64_t N, int64_t K, float alpha, const void* A, int64_t lda,
+                           const void* B, int64_t ldb, float beta, const float* C, int64_t ldc,
+                           float* D, int64_t ldd, const uint32_t* panel_flags, int64_t panel_k);
+
+/* Stream-ordered 32-bit store to device memory (cuStreamWriteValue32): runs without an SM, so it
+ * can signal a kernel that already occupies the whole GPU. */
+int b200_stream_write_u32(b200_stream stream, void* dptr, uint32_t value);
+
+/* Stream-ordered wait (cuStreamWaitValue32, compare >=): work enqueued on `stream` after this
+ * call starts only once the 32-bit word at dptr is >= value.  Together with
+ * b200_stream_write_u32 on a peer-mapped address this orders two GPUs' streams without any
+ * kernel.  The wait has no timeout: only wait for words whose writer is already enqueued. */
+int b200_stream_wait_u32(b200_stream stream, void* dptr, uint32_t value);
+
 /* Same operation with HOST pointers (ideally page-locked): copies A, B and (beta != 0) C to the
  * handle's device workspace, runs the GEMM, copies D back and synchronises before returning.
  * This is the Array -> CuArray -> kernel -> Array(d_dev) round trip of the reference's examples
@@ -215,6 +237,10 @@ int b200_memcpy_h2d(void* dst, const void* src, size_t bytes, b200_stream stream
 int b200_memcpy_d2h(void* dst, const void* src, size_t bytes, b200_stream stream);
 int b200_memset(void* dst, int byte, size_t bytes, b200_stream stream);
 int b200_stream_sync(b200_stream stream);
+/* A new stream that does not synchronise with the legacy default stream (CUDAdrv's CuStream(),
+ * which the reference's `stream` launch keyword takes: src/execution.jl:158-166). */
+int b200_stream_create(b200_stream* out);
+int b200_stream_destroy(b200_stream stream);
 
 /* Peer access for the N-sharded multi-GPU GEMM, one process per GPU (no counterpart in the
  * reference, whose only multi-device facility is picking a device per task: src/init.jl:187-209).

@@ -58,6 +58,7 @@ def main():
     M, N, K = (int(x) for x in sys.argv[2:5])
     panels = int(sys.argv[5]) if len(sys.argv) > 5 else 4
     transport = sys.argv[6] if len(sys.argv) > 6 else "nccl"
+    fused = (sys.argv[7] == "fused") if len(sys.argv) > 7 else False
     seed, alpha, beta = 4, 1.0, 1.0
     rank = int(os.environ["RANK"])
     if backend == "nccl":
@@ -74,7 +75,7 @@ def main():
         dist.init_process_group("gloo")
         handle = OracleHandle()
         dev = torch.device("cpu")
-    sg = ShardedGemm(handle, M, N, K, panels=panels, reserve_ctas=8, sm_count=148, transport=transport)
+    sg = ShardedGemm(handle, M, N, K, panels=panels, reserve_ctas=8, sm_count=148, transport=transport, fused=fused)
     n0, ns = sg.n0, sg.slab_cols
     a_host = rng.matrix(seed, 0, M, K, rng.NORMAL, K ** -0.5, np.float16)
     b_host = rng.window(seed, 1, K, 0, K, n0, n0 + ns, rng.NORMAL, K ** -0.5, np.float16)
@@ -102,7 +103,7 @@ def main():
         d = D.cpu().numpy().T
         oracle.assert_close(d, oracle.gemm_ref(False, False, alpha, a_host, b_host, beta, c_host), f"rank {rank} slab [{n0},{n0 + ns})")
     if backend != "nccl" and ns:
-        want = [(k1 - k0) for (k0, k1) in sg.panels]
+        want = [sg.panels[p1 - 1][1] - sg.panels[p0][0] for (p0, p1) in sg.groups]
         got = [k for (k, _) in handle.calls[:len(want)]]
         assert got == want, (got, want)
         caps = [c for (_, c) in handle.calls[:len(want)]]

@@ -218,6 +218,64 @@ def test_config3_8192_cubed_properties(handle, oracle):
     assert np.array_equal(Array(d2), np.float32(2.0) * Array(d))
 
 
+def _streams(lib, n):
+    import ctypes as C
+    out = []
+    for _ in range(n):
+        s = C.c_void_p()
+        _lib.check(lib.b200_stream_create(C.byref(s)), "stream_create")
+        out.append(s)
+    return out
+
+
+def test_gated_gemm_waits_for_panel_flags(handle, oracle, lib):
+    """The gated GEMM reads a K panel of A only after its flag word is set.  Here the flags are
+    written from a second stream by stream memory operations while the kernel is already running,
+    with the panel's data uploaded just before its flag: a panel read early would see zeros."""
+    import time
+    M, N, K, panel_k = 512, 768, 1024, 256
+    a, b, c = operands(M, N, K, False, False, seed=111)
+    a_dev = CuArray(np.zeros_like(a))              # A starts empty on the device
+    b_dev, c_dev = CuArray(b), CuArray(c)
+    d_dev = CuHostArray(np.float32, shape=(M, N))
+    flags = CuArray(np.zeros(32, dtype=np.float32))  # 32 zero words
+    s_gemm, s_copy = _streams(lib, 2)
+    force(handle, _lib.KERNEL_AUTO)
+    handle.set_option(_lib.OPT_WAIT_BUDGET_NS, 1_000_000_000)
+    handle.gemm_gated(False, False, M, N, K, 1.5, a_dev, M, b_dev, K, 0.5, c_dev, M, d_dev, M, flags, panel_k, stream=s_gemm)
+    for j in range(K // panel_k):                  # the kernel is spinning on flag j by now
+        time.sleep(0.002)
+        cols = np.ascontiguousarray(a[:, j * panel_k:(j + 1) * panel_k].T).T  # Fortran slice, contiguous
+        _lib.check(lib.b200_memcpy_h2d(a_dev.ptr + 2 * j * panel_k * M, cols.ctypes.data, cols.nbytes, s_copy), "upload panel")
+        _lib.check(lib.b200_stream_write_u32(s_copy, flags.ptr + 4 * j, 1), "open gate")
+        _lib.check(lib.b200_stream_sync(s_copy), "sync")  # `cols` must outlive the copy
+    _lib.check(lib.b200_stream_sync(s_gemm), "sync")
+    assert handle.device_status()[0] == 0
+    oracle.assert_close(Array(d_dev), oracle.gemm_ref(False, False, 1.5, a, b, 0.5, c), "gated gemm")
+    # flags already set: behaves like the plain entry point (bit-identical)
+    d2 = CuHostArray(np.float32, shape=(M, N))
+    handle.gemm_gated(False, False, M, N, K, 1.5, a_dev, M, b_dev, K, 0.5, c_dev, M, d2, M, flags, panel_k, stream=s_gemm)
+    _lib.check(lib.b200_stream_sync(s_gemm), "sync")
+    assert np.array_equal(Array(d2), Array(d_dev))
+    # a gate that never opens: the wait runs out, is reported, and the context stays usable
+    _lib.check(lib.b200_memset(flags.ptr, 0, 128, s_copy), "memset")
+    _lib.check(lib.b200_stream_sync(s_copy), "sync")
+    handle.set_option(_lib.OPT_WAIT_BUDGET_NS, 5_000_000)
+    handle.gemm_gated(False, False, M, N, K, 1.5, a_dev, M, b_dev, K, 0.5, c_dev, M, d2, M, flags, panel_k, stream=s_gemm)
+    _lib.check(lib.b200_stream_sync(s_gemm), "sync")
+    code, _, _ = handle.device_status()
+    # the producer's gate wait (108) and the waits of the roles it starves (MMA 102, epilogue 104)
+    # run out together; whichever reports first wins the status word
+    assert code in (108, 102, 104)
+    handle.set_option(_lib.OPT_WAIT_BUDGET_NS, 200_000_000)
+    d3 = run_gemm(handle, False, False, M, N, K, 1.5, a, b, 0.5, c)
+    oracle.assert_close(d3, oracle.gemm_ref(False, False, 1.5, a, b, 0.5, c), "after a closed gate")
+    for s in (s_gemm, s_copy):
+        lib.b200_stream_destroy(s)
+    with pytest.raises(Exception, match="multiple of 64"):
+        handle.gemm_gated(False, False, M, N, K, 1.0, a_dev, M, b_dev, K, 0.0, None, M, d2, M, flags, 100)
+
+
 def test_bounded_wait_reports_and_context_survives(handle, oracle):
     """A wait nothing satisfies runs out after its budget, the status word names it, and the
     context is still usable afterwards."""

@@ -7,7 +7,7 @@ from pathlib import Path
 
 import pytest
 
-from cudanative_jl_b200.gemm import panel_bounds, slab_bounds
+from cudanative_jl_b200.gemm import launch_groups, panel_bounds, slab_bounds
 
 ROOT = Path(__file__).resolve().parent.parent
 
@@ -31,6 +31,15 @@ def test_panels_partition_k(k, panels):
     for (a0, a1), (b0, b1) in zip(b, b[1:]):
         assert a1 == b0 and a1 > a0
     assert all(k0 % 64 == 0 for (k0, _) in b)
+
+
+@pytest.mark.parametrize("n", [1, 2, 3, 8, 16, 32])
+def test_launch_groups_cover_the_panels_and_grow(n):
+    g = launch_groups(n)
+    assert g[0][0] == 0 and g[-1][1] == n
+    assert all(a1 == b0 and a1 > a0 for (a0, a1), (b0, _) in zip(g, g[1:]))
+    sizes = [b - a for (a, b) in g]
+    assert sizes[0] == 1 and sizes == sorted(sizes) and len(g) <= 5
 
 
 @pytest.mark.parametrize("world,shape", [(2, (96, 640, 200)), (3, (64, 512, 130))])
