@@ -55,6 +55,8 @@ SIGNATURES = {
     "b200_host_free": (_i, [_p]),
     "b200_memcpy_h2d": (_i, [_p, _p, _sz, _p]),
     "b200_memcpy_d2h": (_i, [_p, _p, _sz, _p]),
+    "b200_p2p_begin": (_i, [_i, _i, _pp, C.c_uint32, _p, _p, _p]),
+    "b200_p2p_exchange": (_i, [_i, _i, _i64, C.POINTER(_i64), _i, _i, _pp, _pp, C.c_uint32, _p, _p, _p, _p]),
     "b200_ipc_get_handle": (_i, [_p, _p]),
     "b200_ipc_open_handle": (_i, [_p, _pp]),
     "b200_ipc_close_handle": (_i, [_p]),

@@ -369,6 +369,142 @@ int b200_stream_wait_u32(b200_stream stream, void* dptr, uint32_t value) {
     return B200_OK;
 }
 
+}  // extern "C"
+
+namespace {
+
+// flag block layout (32-bit words): done[64] | scattered[32] (+32 spare) | gathered[32][64]
+inline size_t word_done(int g) { return 4u * static_cast<size_t>(g); }
+inline size_t word_scat(int p) { return 4u * (64u + static_cast<size_t>(p)); }
+inline size_t word_gath(int p, int g) { return 4u * (128u + static_cast<size_t>(p) * 64u + static_cast<size_t>(g)); }
+
+using BatchFn = CUresult (*)(CUstream, unsigned int, CUstreamBatchMemOpParams*, unsigned int);
+
+BatchFn batch_fn() {
+    static BatchFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuStreamBatchMemOp", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<BatchFn>(p);
+    }
+    return fn;
+}
+
+// One driver call for a list of 32-bit waits (>=) or writes on a stream.
+struct MemOps {
+    std::vector<CUstreamBatchMemOpParams> ops;
+    void wait(void* base, size_t off, uint32_t value) {
+        CUstreamBatchMemOpParams o;
+        std::memset(&o, 0, sizeof(o));
+        o.waitValue.operation = CU_STREAM_MEM_OP_WAIT_VALUE_32;
+        o.waitValue.address = reinterpret_cast<CUdeviceptr>(static_cast<char*>(base) + off);
+        o.waitValue.value = value;
+        o.waitValue.flags = CU_STREAM_WAIT_VALUE_GEQ;
+        ops.push_back(o);
+    }
+    void write(void* base, size_t off, uint32_t value) {
+        CUstreamBatchMemOpParams o;
+        std::memset(&o, 0, sizeof(o));
+        o.writeValue.operation = CU_STREAM_MEM_OP_WRITE_VALUE_32;
+        o.writeValue.address = reinterpret_cast<CUdeviceptr>(static_cast<char*>(base) + off);
+        o.writeValue.value = value;
+        o.writeValue.flags = 0;
+        ops.push_back(o);
+    }
+    int flush(b200_stream stream, const char* what) {
+        if (ops.empty()) return B200_OK;
+        BatchFn fn = batch_fn();
+        if (!fn) return fail(B200_CUDA_ERROR, "cuStreamBatchMemOp entry point not found");
+        for (size_t i = 0; i < ops.size(); i += 128) {
+            const unsigned n = static_cast<unsigned>(std::min<size_t>(128, ops.size() - i));
+            CUresult r = fn(static_cast<CUstream>(stream), n, ops.data() + i, 0);
+            if (r != CUDA_SUCCESS)
+                return fail(B200_CUDA_ERROR, std::string("cuStreamBatchMemOp failed for ") + what + " (CUresult " +
+                                                 std::to_string(static_cast<int>(r)) + ")");
+        }
+        ops.clear();
+        return B200_OK;
+    }
+};
+
+}  // namespace
+
+extern "C" {
+
+int b200_p2p_begin(int rank, int world, void* const* flag_peers, uint32_t epoch, b200_stream compute,
+                   b200_stream scatter, b200_stream gather) {
+    if (world < 2 || world > 64 || rank < 0 || rank >= world || !flag_peers) return fail(B200_INVALID_ARG, "p2p_begin: bad rank / world");
+    int rc;
+    MemOps tell;
+    for (int g = 0; g < world; ++g)
+        if (g != rank) tell.write(flag_peers[g], word_done(rank), epoch);
+    if ((rc = tell.flush(compute, "done flags"))) return rc;
+    for (int which = 0; which < 2; ++which) {
+        if (which == 0 && rank != 0) continue;  // only rank 0 scatters
+        MemOps hear;
+        for (int g = 0; g < world; ++g)
+            if (g != rank) hear.wait(flag_peers[rank], word_done(g), epoch);
+        if ((rc = hear.flush(which == 0 ? scatter : gather, "done waits"))) return rc;
+    }
+    return B200_OK;
+}
+
+int b200_p2p_exchange(int rank, int world, int64_t M, const int64_t* sub_cols, int p0, int p1, void* const* a_peers,
+                      void* const* flag_peers, uint32_t epoch, b200_stream compute, b200_stream scatter,
+                      b200_stream gather, uint32_t* gate_words) {
+    if (world < 2 || world > 64 || rank < 0 || rank >= world || !a_peers || !flag_peers || !sub_cols)
+        return fail(B200_INVALID_ARG, "p2p_exchange: bad rank / world / tables");
+    if (p0 < 0 || p1 > 32 || p0 > p1 || M <= 0) return fail(B200_INVALID_ARG, "p2p_exchange: bad panel range");
+    int rc;
+    auto copy_cols = [&](int dst, int64_t c0, int64_t c1, b200_stream st) -> int {
+        if (c1 <= c0) return B200_OK;
+        char* d = static_cast<char*>(a_peers[dst]) + 2 * c0 * M;
+        const char* s = static_cast<const char*>(a_peers[rank]) + 2 * c0 * M;
+        B200_CUDA_TRY(cudaMemcpyAsync(d, s, static_cast<size_t>(2 * (c1 - c0) * M), cudaMemcpyDefault, static_cast<cudaStream_t>(st)));
+        return B200_OK;
+    };
+    for (int p = p0; p < p1; ++p) {
+        const int64_t* sub = sub_cols + static_cast<size_t>(p) * world * 2;
+        if (rank == 0) {  // scatter: sub-block g goes to rank g
+            MemOps done;
+            for (int g = 1; g < world; ++g) {
+                if ((rc = copy_cols(g, sub[2 * g], sub[2 * g + 1], scatter))) return rc;
+                done.write(flag_peers[g], word_scat(p), epoch);
+            }
+            if ((rc = done.flush(scatter, "scatter flags"))) return rc;
+        } else {          // my sub-block must be here before I can pass it on
+            MemOps got;
+            got.wait(flag_peers[rank], word_scat(p), epoch);
+            if ((rc = got.flush(gather, "scatter wait"))) return rc;
+        }
+        {   // all-gather: my sub-block goes to everybody but rank 0, which has all of A
+            MemOps done;
+            for (int h = 1; h < world; ++h) {
+                if (h == rank) continue;
+                if ((rc = copy_cols(h, sub[2 * rank], sub[2 * rank + 1], gather))) return rc;
+                done.write(flag_peers[h], word_gath(p, rank), epoch);
+            }
+            if ((rc = done.flush(gather, "all-gather flags"))) return rc;
+        }
+        if (rank != 0) {
+            // arrival of panel p on this rank: my own sub-block (scatter) and everybody else's
+            MemOps here;
+            here.wait(flag_peers[rank], word_scat(p), epoch);
+            for (int g = 0; g < world; ++g)
+                if (g != rank) here.wait(flag_peers[rank], word_gath(p, g), epoch);
+            if (gate_words) {
+                MemOps gate = here;
+                gate.write(gate_words, 4u * static_cast<size_t>(p), 1u);
+                if ((rc = gate.flush(gather, "panel gate"))) return rc;
+            }
+            if ((rc = here.flush(compute, "panel waits"))) return rc;
+        }
+    }
+    return B200_OK;
+}
+
 int b200_gemm_f16f32_host(b200_handle* h, int transA, int transB, int64_t M, int64_t N, int64_t K, float alpha,
                           const void* A, int64_t lda, const void* B, int64_t ldb, float beta, const float* C,
                           int64_t ldc, float* D, int64_t ldd) {

@@ -291,14 +291,7 @@ class ShardedGemm:
     def slab_cols(self) -> int:
         return self.n1 - self.n0
 
-    # flag words (uint32 each) in every rank's flag buffer
-    def _w_done(self, g):      # rank g has finished everything that touched A in the previous call
-        return 4 * g
-    def _w_scat(self, p):      # my sub-block of panel p has arrived from rank 0
-        return 4 * (64 + p)
-    def _w_gath(self, p, g):   # rank g's sub-block of panel p has arrived
-        return 4 * (128 + p * 64 + g)
-    _FLAG_BYTES = 4 * (128 + 32 * 64)
+    _FLAG_BYTES = 4 * (128 + 32 * 64)  # B200_P2P_FLAG_BYTES
 
     # ------------------------------------------------------------------------------------------
     def alloc_a(self):
@@ -338,6 +331,16 @@ class ShardedGemm:
         self._scatter_stream = torch.cuda.Stream()
         self._gather_stream = torch.cuda.Stream()
         self._gate_words = torch.zeros(self.MAX_PANELS, dtype=torch.int32, device=dev)
+        # tables the C side walks: every rank's A and flag block, and the sub-block column ranges
+        G, P = self.world, len(self.panels)
+        self._a_table = (C.c_void_p * G)(*[self._raw.ptr if g == self.rank else self._peers[g] for g in range(G)])
+        self._flag_table = (C.c_void_p * G)(*[self._raw_flags.ptr if g == self.rank else self._peer_flags[g] for g in range(G)])
+        cols = []
+        for (k0, k1) in self.panels:
+            for g in range(G):
+                c0, c1 = slab_bounds(k1 - k0, G, g, align=8)
+                cols += [k0 + c0, k0 + c1]
+        self._sub_cols = (C.c_int64 * (2 * G * P))(*cols)
         return self.A
 
     def close(self) -> None:
@@ -354,75 +357,23 @@ class ShardedGemm:
         self._raw = self._raw_flags = None
 
     # ------------------------------------------------------------------------------------------
-    def _send_panels_p2p(self, a_addr: int, cur_stream: int) -> int:
-        """Enqueue the scatter + all-gather of every K panel on the two transfer streams and the
-        flag writes that announce them.  Returns the epoch the flag words will carry."""
-        torch, L = self.torch, _lib.lib()
-        M, G, r = self.M, self.world, self.rank
-        s1, s2 = self._scatter_stream, self._gather_stream
-        flags = self._raw_flags.ptr
-        self._epoch += 1
-        e = self._epoch
-
-        def write(stream, addr):
-            _lib.check(L.b200_stream_write_u32(stream, addr, e), "flag write")
-
-        def wait(stream, addr):
-            _lib.check(L.b200_stream_wait_u32(stream, addr, e), "flag wait")
-
-        def copy(stream, dst_rank, c0, c1):
-            _lib.check(L.b200_memcpy_d2d(self._peers[dst_rank] + 2 * c0 * M, a_addr + 2 * c0 * M, 2 * (c1 - c0) * M,
-                                         stream), "panel copy")
-
-        # Everything the caller enqueued so far (the previous product reading A, a refill of A on
-        # rank 0) precedes "I am done with my A": tell every peer, then wait until every peer says so.
-        for g in range(G):
-            if g != r:
-                write(cur_stream, self._peer_flags[g] + self._w_done(r))
+    def _p2p_begin(self, cur_stream) -> int:
+        """Start a product: new epoch, 'done with my A' handshake with every peer (b200_p2p_begin)."""
+        torch = self.torch
         cur = torch.cuda.current_stream()
-        s1.wait_stream(cur)
-        s2.wait_stream(cur)
-        for st in ((s1, s2) if r == 0 else (s2,)):
-            for g in range(G):
-                if g != r:
-                    wait(st.cuda_stream, flags + self._w_done(g))
-        if self.fused:  # re-arm the gates of the one-launch form
-            _lib.check(L.b200_memset(self._gate_words.data_ptr(), 0, 4 * self.MAX_PANELS, cur_stream), "reset gates")
-            s2.wait_stream(cur)
-        for p, (k0, k1) in enumerate(self.panels):
-            sub = [(k0 + c0, k0 + c1) for (c0, c1) in (slab_bounds(k1 - k0, G, g, align=8) for g in range(G))]
-            if r == 0:  # scatter: sub-block g goes to rank g
-                for g in range(1, G):
-                    c0, c1 = sub[g]
-                    if c1 > c0:
-                        copy(s1.cuda_stream, g, c0, c1)
-                    write(s1.cuda_stream, self._peer_flags[g] + self._w_scat(p))
-            else:
-                wait(s2.cuda_stream, flags + self._w_scat(p))
-            c0, c1 = sub[r]  # all-gather: my sub-block goes to everybody but rank 0, which has it all
-            for h in range(1, G):
-                if h != r:
-                    if c1 > c0:
-                        copy(s2.cuda_stream, h, c0, c1)
-                    write(s2.cuda_stream, self._peer_flags[h] + self._w_gath(p, r))
-            if self.fused and r != 0:
-                for g in range(G):
-                    if g != r:
-                        wait(s2.cuda_stream, flags + self._w_gath(p, g))
-                write_gate = self._gate_words.data_ptr() + 4 * p
-                _lib.check(L.b200_stream_write_u32(s2.cuda_stream, write_gate, 1), "open panel gate")
-        return e
+        self._scatter_stream.wait_stream(cur)
+        self._gather_stream.wait_stream(cur)
+        self._epoch += 1
+        _lib.check(_lib.lib().b200_p2p_begin(self.rank, self.world, self._flag_table, self._epoch, cur_stream,
+                                             self._scatter_stream.cuda_stream, self._gather_stream.cuda_stream), "p2p_begin")
+        return self._epoch
 
-    def _wait_panels(self, stream: int, p0: int, p1: int, e: int) -> None:
-        """Order `stream` behind the arrival of panels [p0, p1) on this rank."""
-        if self.rank == 0:
-            return  # rank 0 holds all of A from the start
-        L, flags = _lib.lib(), self._raw_flags.ptr
-        for p in range(p0, p1):
-            _lib.check(L.b200_stream_wait_u32(stream, flags + self._w_scat(p), e), "flag wait")
-            for g in range(self.world):
-                if g != self.rank:
-                    _lib.check(L.b200_stream_wait_u32(stream, flags + self._w_gath(p, g), e), "flag wait")
+    def _p2p_exchange(self, cur_stream, p0: int, p1: int, gates=None) -> None:
+        """Enqueue the transfer of panels [p0, p1) and order `cur_stream` behind their arrival here."""
+        _lib.check(_lib.lib().b200_p2p_exchange(self.rank, self.world, self.M, self._sub_cols, p0, p1, self._a_table,
+                                                self._flag_table, self._epoch, cur_stream,
+                                                self._scatter_stream.cuda_stream, self._gather_stream.cuda_stream,
+                                                gates), "p2p_exchange")
 
     def run(self, alpha: float, A, B_slab, beta: float, C_slab, D_slab, stream=None) -> None:
         """A: device buffer of M*K float16 on every rank (contents valid on rank 0 only before the
@@ -438,12 +389,12 @@ class ShardedGemm:
             s = stream
         else:
             s = torch.cuda.current_stream().cuda_stream if a_flat.is_cuda else None
-        works, epoch = [], 0
+        works = []
         p2p = self.world > 1 and self.transport == "p2p"
         if p2p:
             if self._raw is None or a_addr != self._raw.ptr:
                 raise ValueError("the p2p transport needs A in the buffer returned by alloc_a()")
-            epoch = self._send_panels_p2p(a_addr, s)
+            self._p2p_begin(s)
         elif self.world > 1:
             for (k0, k1) in self.panels:
                 view = a_flat[k0 * M:k1 * M]
@@ -457,19 +408,22 @@ class ShardedGemm:
         reserved = max(2, (self.sm_count - self.reserve_ctas) // 2 * 2) if self.reserve_ctas else saved
         try:
             if self.fused and p2p:
+                # one launch: the producer warps wait for the panel gates themselves; the transfers are
+                # enqueued behind the launch so that the waits they put on this stream follow it
+                L = _lib.lib()
+                gates = self._gate_words.data_ptr()
+                _lib.check(L.b200_memset(gates, 1 if self.rank == 0 else 0, 4 * self.MAX_PANELS, s), "arm gates")
+                self._gather_stream.wait_stream(torch.cuda.current_stream())
                 if ns:
-                    # one launch: the producer warps wait for the panel gates themselves
                     h.set_option(_lib.OPT_MAX_CTAS, reserved)
-                    if self.rank == 0:  # rank 0 has all of A: open every gate at once
-                        _lib.check(_lib.lib().b200_memset(self._gate_words.data_ptr(), 1, 4 * self.MAX_PANELS, s), "open gates")
                     h.gemm_gated(False, False, M, ns, K, alpha, a_addr, M, b_addr, K, beta, c_addr, M, d_addr, M,
-                                 self._gate_words.data_ptr(), self.panel_k, stream=s)
-                self._wait_panels(s, 0, len(self.panels), epoch)  # later work on this stream sees all of A
+                                 gates, self.panel_k, stream=s)
+                self._p2p_exchange(s, 0, len(self.panels), gates)
                 return
             for i, (p0, p1) in enumerate(self.groups):
                 last = i == len(self.groups) - 1
                 if p2p:
-                    self._wait_panels(s, p0, p1, epoch)
+                    self._p2p_exchange(s, p0, p1)  # transfers of this group, then the waits for them
                 else:
                     for w in works[p0:p1]:
                         w.wait()  # stream-level: the GEMM below is ordered after these panels

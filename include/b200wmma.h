@@ -254,6 +254,33 @@ int b200_ipc_open_handle(const void* handle64, void** dptr);
 int b200_ipc_close_handle(void* dptr);
 int b200_memcpy_d2d(void* dst, const void* src, size_t bytes, b200_stream stream);
 
+/* Transfer schedule of the N-sharded GEMM (no counterpart in the reference).  A (M rows,
+ * column-major, binary16) starts on rank 0 and travels in K panels: rank 0 copies sub-block g of
+ * a panel into rank g's A (scatter), every rank then copies its own sub-block into every other
+ * rank's A (all-gather); copies run on the copy engines.  Behind each copy the sending stream
+ * writes `epoch` into a flag word in the receiver's flag block, and receiving streams wait for
+ * those words (stream memory operations; no kernel, no SM).
+ *
+ * a_peers / flag_peers: `world` device addresses, entry r = this rank's own buffers, the others
+ * IPC-mapped.  The flag block is B200_P2P_FLAG_BYTES of zero-initialised device memory.
+ * sub_cols: for every panel p and rank g the column range [c0, c1) of sub-block g, as
+ * sub_cols[(p * world + g) * 2 + {0, 1}].
+ *
+ * b200_p2p_begin   : once per product, first: announces on `compute` that this rank no longer
+ *                    touches its A from earlier work and makes `scatter` (rank 0) and `gather`
+ *                    wait until every peer has announced the same for `epoch`.
+ * b200_p2p_exchange: enqueues the copies and flag writes of panels [p0, p1) on `scatter` /
+ *                    `gather`, and on `compute` the waits for the arrival of those panels here.
+ *                    gate_words != NULL additionally writes 1 to gate_words[p] on `gather` once
+ *                    panel p is complete here (the flags b200_gemm_f16f32_gated polls). */
+#define B200_P2P_FLAG_BYTES (4 * (128 + 32 * 64))
+int b200_p2p_begin(int rank, int world, void* const* flag_peers, uint32_t epoch, b200_stream compute,
+                   b200_stream scatter, b200_stream gather);
+int b200_p2p_exchange(int rank, int world, int64_t M, const int64_t* sub_cols, int p0, int p1,
+                      void* const* a_peers, void* const* flag_peers, uint32_t epoch,
+                      b200_stream compute, b200_stream scatter, b200_stream gather,
+                      uint32_t* gate_words);
+
 /* Counter-based synthetic matrices (no counterpart in the reference, whose tests draw from
  * Julia's unseeded rand; test/device/wmma.jl:196-199).  Element (i, j) of a rows x cols
  * column-major matrix gets
