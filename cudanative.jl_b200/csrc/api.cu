@@ -481,8 +481,11 @@ int b200_p2p_exchange(int rank, int world, int64_t M, const int64_t* sub_cols, i
         }
         {   // all-gather: my sub-block goes to everybody but rank 0, which has all of A
             MemOps done;
-            for (int h = 1; h < world; ++h) {
-                if (h == rank) continue;
+            // destinations are visited starting after this rank, so that at any moment the senders
+            // aim at different receivers instead of all at the same one
+            for (int i = 1; i < world; ++i) {
+                const int h = (rank + i) % world;
+                if (h == 0) continue;
                 if ((rc = copy_cols(h, sub[2 * rank], sub[2 * rank + 1], gather))) return rc;
                 done.write(flag_peers[h], word_gath(p, rank), epoch);
             }

@@ -335,10 +335,13 @@ class ShardedGemm:
         G, P = self.world, len(self.panels)
         self._a_table = (C.c_void_p * G)(*[self._raw.ptr if g == self.rank else self._peers[g] for g in range(G)])
         self._flag_table = (C.c_void_p * G)(*[self._raw_flags.ptr if g == self.rank else self._peer_flags[g] for g in range(G)])
+        # A panel is cut into G - 1 sub-blocks, one per receiving rank: rank 0 then sends every byte
+        # of A exactly once (its link is the bottleneck of the scatter) and forwards nothing.
         cols = []
         for (k0, k1) in self.panels:
-            for g in range(G):
-                c0, c1 = slab_bounds(k1 - k0, G, g, align=8)
+            cols += [k0, k0]  # rank 0 owns no sub-block
+            for g in range(1, G):
+                c0, c1 = slab_bounds(k1 - k0, G - 1, g - 1, align=8)
                 cols += [k0 + c0, k0 + c1]
         self._sub_cols = (C.c_int64 * (2 * G * P))(*cols)
         return self.A
