@@ -123,44 +123,60 @@ class ClockSampler:
 # ---------------------------------------------------------------------------------------------
 # CPU statement (oracle) legs
 # ---------------------------------------------------------------------------------------------
-def cpu_sample(w, target_seconds=12.0):
-    """Time float32 sgemm on a column slab of the workload sized for ~target_seconds of CPU work.
-    Returns (TFLOP/s, cores, description, seconds)."""
-    oracle = entry.load_oracle()
-    pkg = entry.load_package()
-    rng = pkg.rng
-    M, K, N = w["M"], w["K"], w["N"]
-    cores = os.cpu_count() or 1
-    # full K, rows 0..m_s-1 of A; a narrow probe learns the host's rate, then the slab is sized
-    m_s = min(M, 2048)
-    a16 = rng.window(w["seed"], 0, (K if w["transA"] else M), 0, (K if w["transA"] else m_s), 0,
-                     (m_s if w["transA"] else K), rng.NORMAL, K ** -0.5, np.float16)
-    n_probe = min(N, 256)
-    b16 = rng.window(w["seed"], 1, K, 0, K, 0, n_probe, rng.NORMAL, K ** -0.5 if w["b_rsqrt"] else 1.0, np.float16)
-    c = np.zeros((m_s, n_probe), np.float32, order="F")
-    a32, b32 = a16.astype(np.float32), b16.astype(np.float32)  # the conversion is not part of mul!
-    oracle.gemm_ref_f32(w["transA"], False, w["alpha"], a32, b32, w["beta"], c)  # warm-up (thread pool, pages)
-    t0 = time.perf_counter()
-    oracle.gemm_ref_f32(w["transA"], False, w["alpha"], a32, b32, w["beta"], c)
-    probe_s = time.perf_counter() - t0
-    probe_flops = 2.0 * m_s * n_probe * K
-    rate = probe_flops / max(probe_s, 1e-6)
-    # sample: all of M (up to memory sanity) x n_cols so that the work is ~target_seconds
-    n_cols = int(max(n_probe, min(N, target_seconds * rate / (2.0 * m_s * K))))
-    b16 = rng.window(w["seed"], 1, K, 0, K, 0, n_cols, rng.NORMAL, K ** -0.5 if w["b_rsqrt"] else 1.0, np.float16)
-    b32 = b16.astype(np.float32)
-    c = np.zeros((m_s, n_cols), np.float32, order="F")
-    best = None
-    reps = 3 if (2.0 * m_s * n_cols * K) / rate < 6.0 else 1
-    for _ in range(reps):
+class CpuSample:
+    """float32 sgemm on a bounded slab of the workload: rows 0..m_s-1 of op(A), full K, the first
+    n_cols columns of B and C.  Operands are generated once; ``run()`` times one product."""
+
+    def __init__(self, w, target_seconds=12.0):
+        self.oracle = entry.load_oracle()
+        rng = entry.load_package().rng
+        self.w = w
+        M, K, N = w["M"], w["K"], w["N"]
+        self.cores = os.cpu_count() or 1
+        m_s = min(M, 8192)
+        a16 = rng.window(w["seed"], 0, (K if w["transA"] else M), 0, (K if w["transA"] else m_s), 0,
+                         (m_s if w["transA"] else K), rng.NORMAL, K ** -0.5, np.float16)
+        self.a32 = a16.astype(np.float32)  # the conversion is not part of mul!
+        # a narrow probe learns the host's rate, then the slab is sized for ~target_seconds of work
+        n_probe = min(N, 128)
+        b_scale = K ** -0.5 if w["b_rsqrt"] else 1.0
+        b32 = rng.window(w["seed"], 1, K, 0, K, 0, n_probe, rng.NORMAL, b_scale, np.float16).astype(np.float32)
+        c = np.zeros((m_s, n_probe), np.float32, order="F")
+        self._gemm(b32, c)  # warm-up (thread pool, pages)
         t0 = time.perf_counter()
-        oracle.gemm_ref_f32(w["transA"], False, w["alpha"], a32, b32, w["beta"], c)
+        self._gemm(b32, c)
+        rate = 2.0 * m_s * n_probe * K / max(time.perf_counter() - t0, 1e-6)
+        n_cols = int(max(n_probe, min(N, target_seconds * rate / (2.0 * m_s * K))))
+        self.b32 = rng.window(w["seed"], 1, K, 0, K, 0, n_cols, rng.NORMAL, b_scale, np.float16).astype(np.float32)
+        self.c = np.zeros((m_s, n_cols), np.float32, order="F")
+        self.flops = 2.0 * m_s * n_cols * K
+        self.desc = (f"float32 sgemm (numpy/OpenBLAS) on Float16-rounded inputs, rows 0..{m_s - 1} x cols 0..{n_cols - 1} "
+                     f"x full K={K} of the workload")
+
+    def _gemm(self, b32, c):
+        w = self.w
+        return self.oracle.gemm_ref_f32(w["transA"], False, w["alpha"], self.a32, b32, w["beta"], c)
+
+    def run(self):
+        """One timed product; returns (TFLOP/s, seconds)."""
+        t0 = time.perf_counter()
+        self._gemm(self.b32, self.c)
         dt = time.perf_counter() - t0
-        best = dt if best is None else min(best, dt)
-    flops = 2.0 * m_s * n_cols * K
-    desc = (f"float32 sgemm (numpy/OpenBLAS) on Float16-rounded inputs, rows 0..{m_s - 1} x cols 0..{n_cols - 1} "
-            f"x full K={K} of the workload, best of {reps}")
-    return flops / best / 1e12, cores, desc, best
+        return self.flops / dt / 1e12, dt
+
+
+def cpu_sample(w, target_seconds=12.0):
+    """Best of up to three products of a slab sized for ~target_seconds of CPU work.
+    Returns (TFLOP/s, cores, description, seconds)."""
+    smp = CpuSample(w, target_seconds)
+    best = None
+    for _ in range(3):
+        v, dt = smp.run()
+        if best is None or dt < best[1]:
+            best = (v, dt)
+        if dt > target_seconds / 2:
+            break
+    return best[0], smp.cores, smp.desc + ", best of up to 3", best[1]
 
 
 # ---------------------------------------------------------------------------------------------
@@ -390,14 +406,15 @@ def run_reference(args):
         return
     name = args.workload or ("gemm8192" if world == 1 else "sharded")
     w = WORKLOADS[name]
-    total_budget = 150.0  # seconds for warm-up + steps
-    per = max(1.0, min(12.0, total_budget / (args.steps + max(args.warmup, 1))))
-    vals, secs, desc, cores = [], [], "", 1
-    for i in range(max(args.warmup, 1) + args.steps):
-        v, cores, desc, s = cpu_sample(w, target_seconds=per)
+    total_budget = 120.0  # seconds for warm-up + steps
+    n_runs = args.steps + max(args.warmup, 1)
+    smp = CpuSample(w, target_seconds=max(0.5, min(12.0, total_budget / n_runs)))
+    vals, secs, desc, cores = [], [], smp.desc, smp.cores
+    for i in range(n_runs):
+        v, dt = smp.run()
         if i >= max(args.warmup, 1):
             vals.append(v)
-            secs.append(s)
+            secs.append(dt)
     v = float(np.mean(vals))
     M, N, K = w["M"], w["N"], w["K"]
     out = {
