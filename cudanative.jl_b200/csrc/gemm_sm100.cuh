@@ -169,6 +169,20 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             uint32_t ph = 0;    // its phase bit
             bool ok = true;
             uint32_t panels_seen = p.panel_flags ? 0u : 0xffffffffu;  // bit j: panel j is known to be here
+            // One tile column: every tile of A is read by exactly one CTA (the HBM-bound skinny shape).
+            // Mark those loads evict-first so that the stream of A does not displace B, which every
+            // CTA re-reads from L2.
+            const bool a_once = (p.tiles_n == 1);
+            const uint64_t once_policy = l2_policy_evict_first();
+            auto load_a = [&](uint32_t dst, int x, int y, uint32_t bar) {
+                if constexpr (kPair) {
+                    if (a_once) tma_load_2d_pair_hint(dst, &tmA, x, y, bar, once_policy);
+                    else tma_load_2d_pair(dst, &tmA, x, y, bar);
+                } else {
+                    if (a_once) tma_load_2d_hint(dst, &tmA, x, y, bar, once_policy);
+                    else tma_load_2d(dst, &tmA, x, y, bar);
+                }
+            };
 #ifdef B200_PROBE_SKIP_LOADS
             uint32_t issued = 0;
 #endif
@@ -202,10 +216,10 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                         const uint32_t fb = full_bar(s);
                         mbar_arrive_expect_tx(fb, Cfg::STAGE_BYTES);
                         if constexpr (kAMn) {
-                            tma_load_2d(sa, &tmA, m0, k0, fb);
-                            tma_load_2d(sa + 8192, &tmA, m0 + 64, k0, fb);
+                            load_a(sa, m0, k0, fb);
+                            load_a(sa + 8192, m0 + 64, k0, fb);
                         } else {
-                            tma_load_2d(sa, &tmA, k0, m0, fb);
+                            load_a(sa, k0, m0, fb);
                         }
                         if constexpr (kBMn) {
 #pragma unroll
@@ -223,10 +237,10 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                         const uint32_t fb = mapa_shared(full_bar(s), 0);
                         if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(s), 2 * Cfg::STAGE_BYTES);
                         if constexpr (kAMn) {
-                            tma_load_2d_pair(sa, &tmA, m0, k0, fb);
-                            tma_load_2d_pair(sa + 8192, &tmA, m0 + 64, k0, fb);
+                            load_a(sa, m0, k0, fb);
+                            load_a(sa + 8192, m0 + 64, k0, fb);
                         } else {
-                            tma_load_2d_pair(sa, &tmA, k0, m0, fb);
+                            load_a(sa, k0, m0, fb);
                         }
                         if constexpr (kBMn) {
 #pragma unroll
@@ -308,12 +322,14 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
         auto chunks_of = [&](int n0) { return min(Cfg::NCHUNK, (p.N - n0 + Cfg::EPI_COLS - 1) / Cfg::EPI_COLS); };
 
+        // C is read once and D written once: keep them from displacing the shared A / B panels in L2
+        const uint64_t stream_policy = l2_policy_evict_first();
         uint32_t g = 0;  // chunk counter: staging buffer g & 1, C-barrier phase (g >> 1) & 1
         if (has_c && elected && unit_first < num_units) {
             int m0, n0, kb0, kb1, out_n0;
             unit_decode(unit_first, m0, n0, kb0, kb1, out_n0);
             mbar_arrive_expect_tx(cfull_bar(0), Cfg::EPI_BYTES);
-            tma_load_2d(epi_base, &tmC, m0, n0, cfull_bar(0));
+            tma_load_2d_hint(epi_base, &tmC, m0, n0, cfull_bar(0), stream_policy);
         }
         uint32_t ucount = 0;
         bool fail = false;
@@ -341,8 +357,8 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                         if (have_next) {
                             tma_store_wait_read<0>();
                             mbar_arrive_expect_tx(cfull_bar(buf ^ 1u), Cfg::EPI_BYTES);
-                            tma_load_2d(epi_base + (buf ^ 1u) * Cfg::EPI_BYTES, &tmC, nm0, nn0,
-                                        cfull_bar(buf ^ 1u));
+                            tma_load_2d_hint(epi_base + (buf ^ 1u) * Cfg::EPI_BYTES, &tmC, nm0, nn0,
+                                             cfull_bar(buf ^ 1u), stream_policy);
                         }
                     } else {
                         tma_store_wait_read<1>();
@@ -372,7 +388,11 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 fail = named_bar_or(2, 128, !ok);
                 if (fail) break;
                 if (elected) {
-                    tma_store_2d(&tmD, m0, out_n0 + j * Cfg::EPI_COLS, epi_base + buf * Cfg::EPI_BYTES);
+                    if (p.split_k > 1)  // partial products are read back by the reduction right away
+                        tma_store_2d(&tmD, m0, out_n0 + j * Cfg::EPI_COLS, epi_base + buf * Cfg::EPI_BYTES);
+                    else
+                        tma_store_2d_hint(&tmD, m0, out_n0 + j * Cfg::EPI_COLS, epi_base + buf * Cfg::EPI_BYTES,
+                                          stream_policy);
                     tma_store_commit();
                 }
             }

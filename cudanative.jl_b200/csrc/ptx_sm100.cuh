@@ -255,6 +255,41 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst_smem, const CUtens
         : "memory");
 }
 
+// L2 eviction policies for streaming data (read or written once, never reused by another CTA):
+// marking it evict-first keeps it from displacing the A / B panels the co-resident CTAs share.
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+
+__device__ __forceinline__ void tma_load_2d_hint(uint32_t dst_smem, const CUtensorMap* tm, int x, int y,
+                                                 uint32_t bar, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+        "[%0], [%1, {%2, %3}], [%4], %5;" ::"r"(dst_smem),
+        "l"(reinterpret_cast<uint64_t>(tm)), "r"(x), "r"(y), "r"(bar), "l"(policy)
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_store_2d_hint(const CUtensorMap* tm, int x, int y, uint32_t src_smem,
+                                                  uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%1, %2}], [%3], %4;" ::"l"(
+            reinterpret_cast<uint64_t>(tm)),
+        "r"(x), "r"(y), "r"(src_smem), "l"(policy)
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_load_2d_pair_hint(uint32_t dst_smem, const CUtensorMap* tm, int x, int y,
+                                                      uint32_t bar_cluster_addr, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+        "[%0], [%1, {%2, %3}], [%4], %5;" ::"r"(dst_smem),
+        "l"(reinterpret_cast<uint64_t>(tm)), "r"(x), "r"(y), "r"(bar_cluster_addr), "l"(policy)
+        : "memory");
+}
+
 // 2-D tiled store shared -> global, tracked by this thread's bulk async-group.
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* tm, int x, int y,
                                              uint32_t src_smem) {
