@@ -378,6 +378,10 @@ def run_ours(args):
                      "frac": round(achieved / peak, 4), "traffic": traffic, "peak_source": f"{peaks['source']} ({peak_kind})",
                      "nominal_frac": round(achieved / (8000.0 if hbm_bound else 2250.0), 4)},
     }
+    if world == 1 and args.workload is None and not args.no_scaling_baseline:
+        # The multi-GPU lines (N > 1) time the sharded 32768 x 32768 x 16384 product; its one-GPU time is measured
+        # here so that the N-GPU values have a like-for-like denominator next to the headline 8192^3 number.
+        out["scaling_baseline"] = sharded_on_one_gpu(h, stream)
     if world == 1 and not args.no_cpu:
         v, cores, desc, secs = cpu_sample(w)
         out["cpu_baseline"] = {"value": round(v, 4), "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": desc,
@@ -390,6 +394,42 @@ def run_ours(args):
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures summarised in
 # profiles/gemm8192_tcgen05_pair_256x256.md and profiles/skinny_tcgen05_128x128.md
 NCU_TRAFFIC = {"gemm8192": 1465122000 + 253011200, "skinny": 270598912 + 4099840}
+
+
+def sharded_on_one_gpu(h, stream, steps=4, warmup=2):
+    """The sharded workload (config 5) on a single GPU: the denominator of the multi-GPU speed-up."""
+    import torch
+    from cudanative_jl_b200 import rng
+
+    w = WORKLOADS["sharded"]
+    M, N, K = w["M"], w["N"], w["K"]
+    A = torch.empty(M * K, dtype=torch.float16, device="cuda")
+    B = torch.empty(K * N, dtype=torch.float16, device="cuda")
+    Cm = torch.empty(M * N, dtype=torch.float32, device="cuda")
+    D = torch.empty(M * N, dtype=torch.float32, device="cuda")
+    rng.fill_device(A.data_ptr(), M, K, M, w["seed"], 0, rng.NORMAL, K ** -0.5, True, stream)
+    rng.fill_device(B.data_ptr(), K, N, K, w["seed"], 1, rng.NORMAL, K ** -0.5, True, stream)
+    rng.fill_device(Cm.data_ptr(), M, N, M, w["seed"], 2, rng.NORMAL, 1.0, False, stream)
+
+    def step():
+        h.gemm(False, False, M, N, K, w["alpha"], A.data_ptr(), M, B.data_ptr(), K, w["beta"], Cm.data_ptr(), M, D.data_ptr(), M,
+               stream=stream)
+    for _ in range(warmup):
+        step()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    ev0.record()
+    for _ in range(steps):
+        step()
+    ev1.record()
+    torch.cuda.synchronize()
+    ms = ev0.elapsed_time(ev1) / steps
+    code, block, _ = h.device_status()
+    if code:
+        raise SystemExit(f"device wait {code} ran out in block {block} in the one-GPU sharded run")
+    del A, B, Cm, D
+    return {"workload": "sharded", "M": M, "N": N, "K": K, "n_gpus": 1, "steps": steps, "ms_per_step": round(ms, 4),
+            "value": round(2.0 * M * N * K / (ms * 1e-3) / 1e12, 2), "unit": "TFLOP/s"}
 
 
 def load_traffic(name):
@@ -443,6 +483,7 @@ def main():
     ap.add_argument("--transport", default="p2p", choices=["p2p", "nccl"], help="how A reaches the other ranks (sharded)")
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-scaling-baseline", action="store_true", help="N=1: skip the one-GPU run of the sharded workload")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
