@@ -20,7 +20,7 @@ BUILD_DIR = PKG_DIR / "build"
 LIB_PATH = PKG_DIR / "libb200wmma.so"
 
 SOURCES = ["api.cu", "gemm_sm100.cu", "gemm_simple.cu", "wmma_unit.cu", "noalloc.cu"]
-HEADERS = ["ptx_sm100.cuh", "gemm_sm100.cuh", "internal.h", "rng.cuh"]
+HEADERS = ["ptx_sm100.cuh", "gemm_sm100.cuh", "internal.h", "rng.cuh", "wmma_frag.cuh"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -75,6 +75,39 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     return LIB_PATH
 
 
+DEVICE_LIB_SRC = CSRC / "wmma_device_lib.cu"
+DEVICE_LIB_OBJ = PKG_DIR / "libb200wmma_device.o"
+DEVICE_LIB_PTX = PKG_DIR / "b200wmma_device.ptx"
+HARNESS_SRC = PKG_DIR.parent / "tests" / "device_lib_harness.cu"
+HARNESS_LIB = PKG_DIR.parent / "tests" / "libdevice_harness.so"
+
+
+def build_device_lib(force: bool = False) -> Path:
+    """The linkable device-side fragment library: a relocatable sm_100a object (for `nvcc -rdc` /
+    nvlink users) and its PTX (for CUDAdrv's CuLink `add_data!`), plus the test harness that links
+    against it the way a foreign kernel would."""
+    nvcc = find_nvcc()
+    deps = [DEVICE_LIB_SRC, CSRC / "wmma_frag.cuh", INCLUDE / "b200wmma.h"]
+    common = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo", "-rdc=true",
+              "-Xcompiler", "-fPIC", "-I", str(INCLUDE)]
+
+    def run(cmd):
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError("nvcc failed:\n" + " ".join(cmd) + "\n" + r.stdout + r.stderr)
+
+    if force or _stale(DEVICE_LIB_OBJ, deps):
+        run([nvcc, *common, "-c", str(DEVICE_LIB_SRC), "-o", str(DEVICE_LIB_OBJ)])
+    if force or _stale(DEVICE_LIB_PTX, deps):
+        run([nvcc, "-arch=compute_100a", "-O3", "-std=c++17", "-rdc=true", "-I", str(INCLUDE), "-ptx", str(DEVICE_LIB_SRC),
+             "-o", str(DEVICE_LIB_PTX)])
+    if force or _stale(HARNESS_LIB, [HARNESS_SRC, DEVICE_LIB_OBJ]):
+        run([nvcc, "-Wno-deprecated-gpu-targets", *common, "-shared", str(HARNESS_SRC), str(DEVICE_LIB_OBJ), "-o", str(HARNESS_LIB),
+             "-lcudart"])
+    return DEVICE_LIB_OBJ
+
+
 if __name__ == "__main__":
     path = build(force="--force" in sys.argv, verbose="-v" in sys.argv)
     print(path)
+    print(build_device_lib(force="--force" in sys.argv))

@@ -125,6 +125,21 @@ int run_gemm(b200_handle* h, cudaStream_t stream, const GemmProblem& g) {
     std::string why;
     const bool eligible = gemm_tcgen05_eligible(g, &why);
     int kernel = h->force_kernel;
+    if (kernel == B200_KERNEL_AUTO && !eligible && (g.M % 4) && g.M > 4 && !g.panel_flags) {
+        // Only the row count stands in the way: give rows [0, M - M % 4) to the tensor-core kernel
+        // and the last one to three rows to the plain kernel.
+        GemmProblem top = g, strip = g;
+        top.M = g.M - g.M % 4;
+        if (gemm_tcgen05_eligible(top, nullptr)) {
+            strip.M = g.M % 4;
+            const int64_t skip = top.M;
+            strip.A = static_cast<const char*>(g.A) + 2 * (g.transA ? skip * g.lda : skip);
+            if (g.C) strip.C = g.C + skip;
+            strip.D = g.D + skip;
+            if ((rc = gemm_simple_launch(strip, stream, nullptr))) return rc;
+            return run_gemm(h, stream, top);
+        }
+    }
     if (kernel == B200_KERNEL_AUTO) kernel = eligible ? B200_KERNEL_TCGEN05 : B200_KERNEL_SIMPLE;
     if (kernel == B200_KERNEL_TCGEN05) {
         if (!eligible) return fail(B200_UNSUPPORTED, "tcgen05 kernel not eligible: " + why);

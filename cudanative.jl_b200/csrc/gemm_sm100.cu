@@ -123,6 +123,9 @@ bool gemm_tcgen05_eligible(const GemmProblem& g, std::string* why) {
     if (g.beta != 0.0f && (reinterpret_cast<uintptr_t>(g.C) & 15u)) return no("C must be 16-byte aligned for TMA");
     if ((g.lda % 8) || (g.ldb % 8)) return no("lda and ldb must be multiples of 8 elements for TMA");
     if ((g.ldd % 4) || (g.beta != 0.0f && (g.ldc % 4))) return no("ldc and ldd must be multiples of 4 elements for TMA");
+    // bulk tensor stores clip at 16-byte granularity: with M % 4 != 0 the last chunk of every column
+    // would spill into the rows M .. roundup(M, 4) - 1 of the caller's buffer
+    if (g.M % 4) return no("M must be a multiple of 4 (bulk stores are 16-byte granular)");
     return true;
 }
 

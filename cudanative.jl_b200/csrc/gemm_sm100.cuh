@@ -199,7 +199,7 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                             panels_seen |= 1u << panel;
                         }
                     }
-                    ok = mbar_wait<false>(empty_bar(s), ph ^ 1u, wc, kWaitEmptyStage);
+                    ok = mbar_wait(empty_bar(s), ph ^ 1u, wc, kWaitEmptyStage);
                     if (!ok) break;
 #ifdef B200_PROBE_SKIP_LOADS
                     // timing probe (results are wrong): after the ring has been filled once,
@@ -277,13 +277,13 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 unit_decode(unit, m0, n0, kb0, kb1, out_n0);
                 const uint32_t acc = ucount & 1u;
                 const uint32_t aph = (ucount >> 1) & 1u;
-                ok = mbar_wait<false>(tmem_empty_bar(acc), aph ^ 1u, wc, kWaitTmemEmpty);
+                ok = mbar_wait(tmem_empty_bar(acc), aph ^ 1u, wc, kWaitTmemEmpty);
                 if (!ok) break;
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + acc * kBN;
                 uint32_t accumulate = 0;
                 for (int kb = kb0; kb < kb1; ++kb, s = (s + 1 == STAGES ? 0 : s + 1), ph ^= (s == 0)) {
-                    ok = mbar_wait<false>(full_bar(s), ph, wc, kWaitFullStage);
+                    ok = mbar_wait(full_bar(s), ph, wc, kWaitFullStage);
                     if (!ok) break;
                     tc_fence_after_sync();
                     const uint64_t da = da0 + static_cast<uint64_t>(s * (Cfg::STAGE_BYTES >> 4));
@@ -339,7 +339,7 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             const int nchunks = chunks_of(n0);
             const uint32_t acc = ucount & 1u;
             const uint32_t aph = (ucount >> 1) & 1u;
-            bool ok = mbar_wait<false>(tmem_full_bar(acc), aph, wc, kWaitTmemFull);
+            bool ok = mbar_wait(tmem_full_bar(acc), aph, wc, kWaitTmemFull);
             tc_fence_after_sync();
             for (int j = 0; j < nchunks; ++j, ++g) {
                 const uint32_t buf = g & 1u;
@@ -387,7 +387,7 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 }
                 fail = named_bar_or(2, 128, !ok);
                 if (fail) break;
-                if (elected) {
+                if (elected && m0 < p.M) {  // a pair's second CTA may own no rows of a bottom-edge tile
                     if (p.split_k > 1)  // partial products are read back by the reduction right away
                         tma_store_2d(&tmD, m0, out_n0 + j * Cfg::EPI_COLS, epi_base + buf * Cfg::EPI_BYTES);
                     else

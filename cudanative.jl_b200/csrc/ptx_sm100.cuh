@@ -60,38 +60,12 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar, uint32_t cta_r
         : "memory");
 }
 
-// arrive + expect_tx on a barrier named by a shared::cluster address (own or peer CTA).
-__device__ __forceinline__ void mbar_arrive_expect_tx_cluster(uint32_t bar_cluster_addr,
-                                                              uint32_t bytes) {
-    asm volatile(
-        "mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(
-            bar_cluster_addr),
-        "r"(bytes)
-        : "memory");
-}
-
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n"
         ".reg .pred p;\n"
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n"
-        "}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-
-// Same, with cluster-scope acquire: for barriers a peer CTA (or an MMA that read the peer's
-// shared memory) completes.
-__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
         "selp.u32 %0, 1, 0, p;\n"
         "}"
         : "=r"(ok)
@@ -137,16 +111,13 @@ static __device__ __noinline__ void report_timeout(const WaitCtx& w, int where, 
 // a microsecond, which a producer that is one stage ahead would pay on every k-block) at two
 // cycles per nanosecond: with SM clocks between 1 and 2 GHz a wait gives up after one to two
 // times budget_ns.
-template <bool kCluster = false>
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx& w,
-                                          int where) {
-    if (kCluster ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx& w, int where) {
+    if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     const long long budget_cycles = static_cast<long long>(w.budget_ns) * 2;
     uint32_t spins = 0;
     for (;;) {
-        if (kCluster ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity))
-            return true;
+        if (mbar_try_wait(bar, parity)) return true;
         if ((++spins & 31u) == 0u) {
             if (*w.abort_flag) return false;
             if (clock64() - t0 > budget_cycles) {

@@ -128,7 +128,8 @@ int b200_last_launch(b200_handle* h, int* kernel, int* tile_n, int* split_k, int
  *   D may alias C exactly (same pointer, same ld).  M, N >= 0; K >= 0 (K == 0: D = beta*C).
  *
  * The tcgen05 kernel needs 16-byte aligned pointers and leading dimensions (lda, ldb
- * multiples of 8 elements; ldc, ldd multiples of 4); anything else runs on the simple kernel. */
+ * multiples of 8 elements; ldc, ldd multiples of 4) and M a multiple of 4; with any other M the
+ * last M % 4 rows run on the simple kernel, and anything else runs on the simple kernel whole. */
 int b200_gemm_f16f32(b200_handle* h, b200_stream stream, int transA, int transB, int64_t M,
                      int64_t N, int64_t K, float alpha, const void* A, int64_t lda, const void* B,
                      int64_t ldb, float beta, const float* C, int64_t ldc, float* D, int64_t ldd);

@@ -1,0 +1,82 @@
+"""The linkable device-side fragment library (csrc/wmma_device_lib.cu): all 52 `extern "C" __device__`
+functions exercised from a foreign kernel (tests/device_lib_harness.cu) that links against the
+relocatable object, checked against the CPU oracle.  Mirrors test/device/wmma.jl:13-151 of
+CUDAnative.jl (llvm_wmma_load / store with all-42 tiles, llvm_wmma_mma over layouts and types)."""
+import ctypes as C
+import itertools
+import re
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from cudanative_jl_b200 import rng
+from cudanative_jl_b200.array import Array, CuArray
+
+ROOT = Path(__file__).resolve().parent.parent
+HARNESS = ROOT / "tests" / "libdevice_harness.so"
+PTX = ROOT / "cudanative.jl_b200" / "b200wmma_device.ptx"
+
+
+def reference_names():
+    """The 52 wrapper names src/device/cuda/wmma.jl:104-257 generates, with the b200_ prefix."""
+    names = []
+    for mat, types in (("a", ["f16"]), ("b", ["f16"]), ("c", ["f16", "f32"])):
+        for lay, as_, ty in itertools.product(["col", "row"], ["", "_global", "_shared"], types):
+            names.append(f"b200_wmma_load_{mat}_{lay}_m16n16k16{as_}_stride_{ty}")
+    for lay, as_, ty in itertools.product(["col", "row"], ["", "_global", "_shared"], ["f16", "f32"]):
+        names.append(f"b200_wmma_store_d_{lay}_m16n16k16{as_}_stride_{ty}")
+    for al, bl, d, c in itertools.product(["col", "row"], ["col", "row"], ["f16", "f32"], ["f16", "f32"]):
+        names.append(f"b200_wmma_mma_{al}_{bl}_m16n16k16_{d}_{c}")
+    return names
+
+
+def test_ptx_exports_the_52_reference_names(pkg):
+    pkg.build.build_device_lib()
+    text = PTX.read_text()
+    exported = set(re.findall(r"\.visible \.func[^\n]*?\b(b200_wmma_[a-z0-9_]+)\(", text)) | \
+        set(re.findall(r"\.visible \.func\s+(b200_wmma_[a-z0-9_]+)\(", text))
+    names = reference_names()
+    assert len(names) == 52
+    assert set(names) <= exported, sorted(set(names) - exported)
+    assert ".target sm_100a" in text
+
+
+@pytest.fixture(scope="module")
+def harness(pkg):
+    pkg.build.build_device_lib()
+    lib = C.CDLL(str(HARNESS))
+    lib.harness_run.restype = C.c_int
+    lib.harness_run.argtypes = [C.c_int] * 7 + [C.c_void_p] * 4
+    return lib
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("as_", [0, 1, 3], ids=["generic", "global", "shared"])
+def test_all_layouts_and_types_through_the_linked_functions(harness, oracle, as_):
+    """16 layout combinations x (C, D) types, per address space: every load, mma and store variant."""
+    for i, (ar, br, cr, dr, ct, dt) in enumerate(itertools.product([0, 1], [0, 1], [0, 1], [0, 1],
+                                                                    [np.float16, np.float32], [np.float16, np.float32])):
+        a = rng.matrix(500 + i, 0, 16, 16, rng.UNIFORM, 1.0, np.float16)
+        b = rng.matrix(500 + i, 1, 16, 16, rng.UNIFORM, 1.0, np.float16)
+        c = rng.matrix(500 + i, 2, 16, 16, rng.UNIFORM, 1.0, ct)
+        a_dev, b_dev, c_dev = CuArray(a), CuArray(b), CuArray(c)
+        d_dev = CuArray(np.zeros((16, 16), dtype=dt, order="F"))
+        rc = harness.harness_run(ar, br, cr, dr, int(ct == np.float16), int(dt == np.float16), as_, a_dev.ptr, b_dev.ptr,
+                                 c_dev.ptr, d_dev.ptr)
+        assert rc == 0, f"cudaError {rc}"
+        ref = oracle.wmma_unit_ref(a, b, c, a_layout=ar, b_layout=br, c_layout=cr, d_layout=dr, d_type=dt)
+        assert oracle.unit_close(Array(d_dev), ref), f"case {i}: layouts {ar}{br}{cr}{dr} C {ct.__name__} D {dt.__name__}"
+
+
+@pytest.mark.gpu
+def test_load_store_identity_with_42(harness):
+    """test/device/wmma.jl:13-100: tiles of 42 go through load and store unchanged (A = 0 so D = C)."""
+    for as_, dr, cr in itertools.product([0, 1, 3], [0, 1], [0, 1]):
+        for ty in (np.float16, np.float32):
+            z = CuArray(np.zeros((16, 16), np.float16, order="F"))
+            c_dev = CuArray(np.full((16, 16), 42, dtype=ty, order="F"))
+            d_dev = CuArray(np.zeros((16, 16), dtype=ty, order="F"))
+            assert harness.harness_run(0, 0, cr, dr, int(ty == np.float16), int(ty == np.float16), as_, z.ptr, z.ptr,
+                                       c_dev.ptr, d_dev.ptr) == 0
+            assert np.all(Array(d_dev) == ty(42))

@@ -62,6 +62,46 @@ def test_ragged_multi_tile(handle, oracle, tA, tB, tile_n, pair):
     oracle.assert_close(d, oracle.gemm_ref(tA, tB, 2.0, a, b, 0.5, c), f"ragged {tile_n}x{pair}")
 
 
+@pytest.mark.parametrize("M,N,K,tile_n,pair", [(300, 300, 192, 256, 2), (300, 300, 192, 128, 2), (64, 48, 64, 64, 1),
+                                               (8, 8, 8, 64, 1), (132, 257, 65 * 8, 256, 1)])
+def test_edge_tiles(handle, oracle, M, N, K, tile_n, pair):
+    """Tiles that hang over the bottom / right edge: in 2-CTA tiles the second CTA may own no valid
+    row at all (M = 300: rows 384..511 of the second tile do not exist)."""
+    force(handle, tile_n=tile_n, pair=pair)
+    for (tA, tB) in LAYOUTS:
+        if tB and (tile_n // pair) % 64:
+            continue
+        # leading dimensions rounded up to what TMA can address, plus canary rows below D
+        a, b, c = operands(M, N, K, tA, tB, seed=77)
+        lda = -(-a.shape[0] // 8) * 8
+        ldb = -(-b.shape[0] // 8) * 8
+        d = run_gemm(handle, tA, tB, M, N, K, 0.5, padded(a, lda, 0), padded(b, ldb, 0), 2.0, padded(c, M + 4, 0), ldd=M + 8)
+        oracle.assert_close(d[:M], oracle.gemm_ref(tA, tB, 0.5, a, b, 2.0, c), f"edge {M}x{N}x{K} tA={tA} tB={tB}")
+        assert np.all(d[M:] == np.float32(-7.25)), "rows beyond M were written"
+
+
+@pytest.mark.parametrize("M", [129, 130, 135, 5, 3])
+def test_row_counts_that_are_not_multiples_of_four(handle, oracle, M):
+    """Bulk stores are 16-byte granular, so the tensor-core kernel takes M - M % 4 rows and the plain
+    kernel the rest: the result is complete and nothing below row M is touched."""
+    force(handle, _lib.KERNEL_AUTO)
+    N, K = 200, 136
+    for (tA, tB) in LAYOUTS:
+        a, b, c = operands(M, N, K, tA, tB, seed=78)
+        lda = -(-a.shape[0] // 8) * 8
+        ldb = -(-b.shape[0] // 8) * 8
+        ld = -(-M // 4) * 4 + 4
+        d = run_gemm(handle, tA, tB, M, N, K, 1.5, padded(a, lda, 0), padded(b, ldb, 0), -1.0, padded(c, ld, 9.0), ldd=ld)
+        oracle.assert_close(d[:M], oracle.gemm_ref(tA, tB, 1.5, a, b, -1.0, c), f"M={M} tA={tA} tB={tB}")
+        assert np.all(d[M:] == np.float32(-7.25)), "rows beyond M were written"
+        if M > 4:
+            assert handle.last_launch()["kernel"] == _lib.KERNEL_TCGEN05
+    force(handle, _lib.KERNEL_TCGEN05)
+    with pytest.raises(Exception, match="multiple of 4"):
+        a, b, c = operands(130, N, K, False, False, seed=78)
+        run_gemm(handle, False, False, 130, N, K, 1.0, padded(a, 136, 0), b, 0.0, None, ldd=136)
+
+
 @pytest.mark.parametrize("tile_n", [128, 256])
 def test_pair_many_stage_wraps(handle, oracle, tile_n):
     """2-CTA tiles with a K loop far longer than the stage ring and several tiles per pair."""
