@@ -38,6 +38,7 @@ SIGNATURES = {
     "b200_selftest_bounded_wait": (_i, [_p, _p, _i64]),
     "b200_last_launch": (_i, [_p, _ip, _ip, _ip, _ip, _ip]),
     "b200_gemm_f16f32": (_i, [_p, _p, _i, _i, _i64, _i64, _i64, _f, _p, _i64, _p, _i64, _f, _p, _i64, _p, _i64]),
+    "b200_gemm_f16_typed": (_i, [_p, _p, _i, _i, _i64, _i64, _i64, _f, _p, _i64, _p, _i64, _f, _p, _i64, _i, _p, _i64, _i]),
     "b200_gemm_f16f32_gated": (_i, [_p, _p, _i, _i, _i64, _i64, _i64, _f, _p, _i64, _p, _i64, _f, _p, _i64, _p, _i64, _p, _i64]),
     "b200_stream_write_u32": (_i, [_p, _p, C.c_uint32]),
     "b200_stream_wait_u32": (_i, [_p, _p, C.c_uint32]),

@@ -125,17 +125,18 @@ int run_gemm(b200_handle* h, cudaStream_t stream, const GemmProblem& g) {
     std::string why;
     const bool eligible = gemm_tcgen05_eligible(g, &why);
     int kernel = h->force_kernel;
-    if (kernel == B200_KERNEL_AUTO && !eligible && (g.M % 4) && g.M > 4 && !g.panel_flags) {
-        // Only the row count stands in the way: give rows [0, M - M % 4) to the tensor-core kernel
-        // and the last one to three rows to the plain kernel.
+    const int64_t m_quant = 16 / elem_bytes(g.d_type);
+    if (kernel == B200_KERNEL_AUTO && !eligible && (g.M % m_quant) && g.M > m_quant && !g.panel_flags) {
+        // Only the row count stands in the way: give the rows that fill whole 16-byte store chunks to
+        // the tensor-core kernel and the last few rows to the plain kernel.
         GemmProblem top = g, strip = g;
-        top.M = g.M - g.M % 4;
+        top.M = g.M - g.M % m_quant;
         if (gemm_tcgen05_eligible(top, nullptr)) {
-            strip.M = g.M % 4;
+            strip.M = g.M % m_quant;
             const int64_t skip = top.M;
             strip.A = static_cast<const char*>(g.A) + 2 * (g.transA ? skip * g.lda : skip);
-            if (g.C) strip.C = g.C + skip;
-            strip.D = g.D + skip;
+            if (g.C) strip.C = reinterpret_cast<const float*>(reinterpret_cast<const char*>(g.C) + skip * elem_bytes(g.c_type));
+            strip.D = reinterpret_cast<float*>(reinterpret_cast<char*>(g.D) + skip * elem_bytes(g.d_type));
             if ((rc = gemm_simple_launch(strip, stream, nullptr))) return rc;
             return run_gemm(h, stream, top);
         }
@@ -326,6 +327,19 @@ int b200_gemm_f16f32(b200_handle* h, b200_stream stream, int transA, int transB,
                      int64_t ldc, float* D, int64_t ldd) {
     if (!h) return fail(B200_INVALID_ARG, "null handle");
     GemmProblem g{transA, transB, M, N, K, alpha, beta, A, lda, B, ldb, C, ldc, D, ldd};
+    return run_gemm(h, static_cast<cudaStream_t>(stream), g);
+}
+
+int b200_gemm_f16_typed(b200_handle* h, b200_stream stream, int transA, int transB, int64_t M, int64_t N, int64_t K,
+                        float alpha, const void* A, int64_t lda, const void* B, int64_t ldb, float beta, const void* C,
+                        int64_t ldc, int c_type, void* D, int64_t ldd, int d_type) {
+    if (!h) return fail(B200_INVALID_ARG, "null handle");
+    if ((c_type != B200_F16 && c_type != B200_F32) || (d_type != B200_F16 && d_type != B200_F32))
+        return fail(B200_INVALID_ARG, "invalid element type for WMMA: C and D must be Float16 or Float32");
+    GemmProblem g{transA, transB, M, N, K, alpha, beta, A, lda, B, ldb, static_cast<const float*>(C), ldc,
+                  static_cast<float*>(D), ldd};
+    g.c_type = c_type;
+    g.d_type = d_type;
     return run_gemm(h, static_cast<cudaStream_t>(stream), g);
 }
 

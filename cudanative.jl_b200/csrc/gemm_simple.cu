@@ -19,8 +19,12 @@ constexpr int kTileK = 16;  // k per shared-memory step
 template <bool kTransA, bool kTransB>
 __global__ void __launch_bounds__(256)
 gemm_simple_kernel(int64_t M, int64_t N, int64_t K, float alpha, const __half* __restrict__ A, int64_t lda,
-                   const __half* __restrict__ B, int64_t ldb, float beta, const float* C, int64_t ldc, float* D,
-                   int64_t ldd) {
+                   const __half* __restrict__ B, int64_t ldb, float beta, const void* Cv, int64_t ldc, void* Dv,
+                   int64_t ldd, int c_f16, int d_f16) {
+    const float* C = static_cast<const float*>(Cv);
+    float* D = static_cast<float*>(Dv);
+    const __half* Ch = static_cast<const __half*>(Cv);
+    __half* Dh = static_cast<__half*>(Dv);
     __shared__ float sA[kTileK][kTile + 1];
     __shared__ float sB[kTileK][kTile + 1];
     const int tx = threadIdx.x & 15;  // 4 rows each
@@ -69,8 +73,9 @@ gemm_simple_kernel(int64_t M, int64_t N, int64_t K, float alpha, const __half* _
             const int64_t m = m0 + tx * 4 + i;
             if (m >= M) continue;
             float v = alpha * acc[i][j];
-            if (beta != 0.0f) v = fmaf(beta, C[m + n * ldc], v);
-            D[m + n * ldd] = v;
+            if (beta != 0.0f) v = fmaf(beta, c_f16 ? __half2float(Ch[m + n * ldc]) : C[m + n * ldc], v);
+            if (d_f16) Dh[m + n * ldd] = __float2half_rn(v);
+            else D[m + n * ldd] = v;
         }
     }
 }
@@ -112,7 +117,8 @@ int gemm_simple_launch(const GemmProblem& g, cudaStream_t stream, LaunchInfo* in
     const __half* A = static_cast<const __half*>(g.A);
     const __half* B = static_cast<const __half*>(g.B);
 #define B200_SIMPLE(TA, TB) \
-    gemm_simple_kernel<TA, TB><<<grid, 256, 0, stream>>>(g.M, g.N, g.K, g.alpha, A, g.lda, B, g.ldb, g.beta, g.C, g.ldc, g.D, g.ldd)
+    gemm_simple_kernel<TA, TB><<<grid, 256, 0, stream>>>(g.M, g.N, g.K, g.alpha, A, g.lda, B, g.ldb, g.beta, g.C, g.ldc, g.D, g.ldd, \
+                                                         g.c_type == B200_F16 ? 1 : 0, g.d_type == B200_F16 ? 1 : 0)
     if (g.transA) { if (g.transB) B200_SIMPLE(true, true); else B200_SIMPLE(true, false); }
     else          { if (g.transB) B200_SIMPLE(false, true); else B200_SIMPLE(false, false); }
 #undef B200_SIMPLE

@@ -122,10 +122,13 @@ bool gemm_tcgen05_eligible(const GemmProblem& g, std::string* why) {
         return no("A, B and D must be 16-byte aligned for TMA");
     if (g.beta != 0.0f && (reinterpret_cast<uintptr_t>(g.C) & 15u)) return no("C must be 16-byte aligned for TMA");
     if ((g.lda % 8) || (g.ldb % 8)) return no("lda and ldb must be multiples of 8 elements for TMA");
-    if ((g.ldd % 4) || (g.beta != 0.0f && (g.ldc % 4))) return no("ldc and ldd must be multiples of 4 elements for TMA");
-    // bulk tensor stores clip at 16-byte granularity: with M % 4 != 0 the last chunk of every column
-    // would spill into the rows M .. roundup(M, 4) - 1 of the caller's buffer
-    if (g.M % 4) return no("M must be a multiple of 4 (bulk stores are 16-byte granular)");
+    const int c_quant = 16 / elem_bytes(g.c_type), d_quant = 16 / elem_bytes(g.d_type);
+    if ((g.ldd % d_quant) || (g.beta != 0.0f && (g.ldc % c_quant)))
+        return no("ldc and ldd must be multiples of 16 bytes for TMA");
+    // bulk tensor stores clip at 16-byte granularity: with a ragged last chunk every column
+    // would spill into the rows M .. roundup(M) - 1 of the caller's buffer
+    if (g.M % d_quant) return no(g.d_type == B200_F16 ? "M must be a multiple of 8 for Float16 D (bulk stores are 16-byte granular)"
+                                                      : "M must be a multiple of 4 (bulk stores are 16-byte granular)");
     return true;
 }
 
@@ -184,12 +187,13 @@ int gemm_tcgen05_launch(const GemmProblem& g, const GemmPlan& plan, float* scrat
         p.beta = 0.0f;
         p.out_n_stride = q.ws_n_stride;
     } else {
-        rc = make_map_2d(&tmD, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, g.D, g.M, g.N, g.ldd, 128, 32,
-                         CU_TENSOR_MAP_SWIZZLE_NONE, "D");
+        const bool dh = g.d_type == B200_F16, ch = g.c_type == B200_F16;
+        rc = make_map_2d(&tmD, dh ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, dh ? 2 : 4, g.D, g.M,
+                         g.N, g.ldd, 128, 32, CU_TENSOR_MAP_SWIZZLE_NONE, "D");
         if (rc) return rc;
         if (g.beta != 0.0f) {
-            rc = make_map_2d(&tmC, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, g.C, g.M, g.N, g.ldc, 128, 32,
-                             CU_TENSOR_MAP_SWIZZLE_NONE, "C");
+            rc = make_map_2d(&tmC, ch ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, ch ? 2 : 4, g.C,
+                             g.M, g.N, g.ldc, 128, 32, CU_TENSOR_MAP_SWIZZLE_NONE, "C");
             if (rc) return rc;
         } else {
             tmC = tmD;  // never dereferenced
@@ -197,6 +201,8 @@ int gemm_tcgen05_launch(const GemmProblem& g, const GemmPlan& plan, float* scrat
         p.alpha = g.alpha;
         p.beta = g.beta;
         p.out_n_stride = 0;
+        p.c_f16 = ch ? 1 : 0;
+        p.d_f16 = dh ? 1 : 0;
     }
 
     const int units = q.tiles_m * q.tiles_n * q.split_k;
@@ -226,14 +232,16 @@ int gemm_tcgen05_launch(const GemmProblem& g, const GemmPlan& plan, float* scrat
     if (rc) return rc;
 
     if (q.split_k > 1) {
-        const bool vec_ok = !((reinterpret_cast<uintptr_t>(g.D) & 15u) || (g.ldd % 4) ||
+        const bool vec_ok = g.c_type == B200_F32 && g.d_type == B200_F32 &&
+                            !((reinterpret_cast<uintptr_t>(g.D) & 15u) || (g.ldd % 4) ||
                               (g.beta != 0.0f && ((reinterpret_cast<uintptr_t>(g.C) & 15u) || (g.ldc % 4))));
         const long long quads = (g.M + 3) / 4 * g.N;
         int blocks = static_cast<int>((quads + 255) / 256);
         if (blocks > sm_count * 8) blocks = sm_count * 8;
         if (blocks < 1) blocks = 1;
         gemm_splitk_reduce<<<blocks, 256, 0, stream>>>(scratch, q.ws_ld, q.ws_n_stride, q.split_k, p.M, p.N, g.alpha,
-                                                       g.beta, g.C, g.ldc, g.D, g.ldd, vec_ok ? 1 : 0);
+                                                       g.beta, g.C, g.ldc, g.D, g.ldd, vec_ok ? 1 : 0, g.c_type == B200_F16 ? 1 : 0,
+                                                       g.d_type == B200_F16 ? 1 : 0);
         B200_CUDA_TRY(cudaGetLastError());
     }
     if (info) {

@@ -45,6 +45,7 @@ struct GemmParams {
     // panel has arrived in this GPU's memory).  At most 32 panels.
     const unsigned int* panel_flags;
     int kb_per_panel;
+    int c_f16, d_f16;      // element types of C and D in memory: 0 = binary32, 1 = binary16
     int* status;
     unsigned long long wait_budget_ns;
 };
@@ -319,6 +320,11 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         const bool elected = (et == 0);
         const bool has_c = (p.beta != 0.0f);
         const float alpha = p.alpha, beta = p.beta;
+        const bool c_f16 = p.c_f16 != 0, d_f16 = p.d_f16 != 0;
+        const uint32_t c_chunk_bytes = c_f16 ? Cfg::EPI_BYTES / 2 : Cfg::EPI_BYTES;
+        // C is updated in place in the staging buffer only if D has the same element size; otherwise
+        // every thread must have read its C values before anybody writes D over them
+        const bool two_phase = has_c && (c_f16 != d_f16);
 
         auto chunks_of = [&](int n0) { return min(Cfg::NCHUNK, (p.N - n0 + Cfg::EPI_COLS - 1) / Cfg::EPI_COLS); };
 
@@ -328,7 +334,7 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         if (has_c && elected && unit_first < num_units) {
             int m0, n0, kb0, kb1, out_n0;
             unit_decode(unit_first, m0, n0, kb0, kb1, out_n0);
-            mbar_arrive_expect_tx(cfull_bar(0), Cfg::EPI_BYTES);
+            mbar_arrive_expect_tx(cfull_bar(0), c_chunk_bytes);
             tma_load_2d_hint(epi_base, &tmC, m0, n0, cfull_bar(0), stream_policy);
         }
         uint32_t ucount = 0;
@@ -356,7 +362,7 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                         }
                         if (have_next) {
                             tma_store_wait_read<0>();
-                            mbar_arrive_expect_tx(cfull_bar(buf ^ 1u), Cfg::EPI_BYTES);
+                            mbar_arrive_expect_tx(cfull_bar(buf ^ 1u), c_chunk_bytes);
                             tma_load_2d_hint(epi_base + (buf ^ 1u) * Cfg::EPI_BYTES, &tmC, nm0, nn0,
                                              cfull_bar(buf ^ 1u), stream_policy);
                         }
@@ -370,18 +376,35 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     named_bar_sync(1, 128);
                 }
                 ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld is warp-collective
+                uint32_t r[32];
+                float* col = epi_gen + buf * (Cfg::EPI_BYTES / 4) + et;                      // binary32 view
+                __half* colh = reinterpret_cast<__half*>(epi_gen + buf * (Cfg::EPI_BYTES / 4)) + et;  // binary16 view
                 if (ok) {
-                    uint32_t r[32];
                     tmem_ld_32x32b_x32(tmem_base + lane_base + acc * kBN + j * Cfg::EPI_COLS, r);
                     tmem_wait_ld();
-                    float* col = epi_gen + buf * (Cfg::EPI_BYTES / 4) + et;
                     if (has_c) {
+                        if (c_f16) {
 #pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            col[i * Cfg::BM] = fmaf(alpha, __uint_as_float(r[i]), beta * col[i * Cfg::BM]);
+                            for (int i = 0; i < 32; ++i)
+                                r[i] = __float_as_uint(fmaf(alpha, __uint_as_float(r[i]), beta * __half2float(colh[i * Cfg::BM])));
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                r[i] = __float_as_uint(fmaf(alpha, __uint_as_float(r[i]), beta * col[i * Cfg::BM]));
+                        }
                     } else {
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) col[i * Cfg::BM] = alpha * __uint_as_float(r[i]);
+                        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(alpha * __uint_as_float(r[i]));
+                    }
+                }
+                if (two_phase) named_bar_sync(3, 128);
+                if (ok) {
+                    if (d_f16) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) colh[i * Cfg::BM] = __float2half_rn(__uint_as_float(r[i]));
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) col[i * Cfg::BM] = __uint_as_float(r[i]);
                     }
                     fence_proxy_async_smem();
                 }
@@ -424,11 +447,15 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 }
 
 // D[m, n] = alpha * sum_s ws[m, n + s * n_stride] + beta * C[m, n]; ws column-major with ldw.
-// Four rows per thread (M-contiguous float4 when everything is 16-byte aligned).
+// Four rows per thread (M-contiguous float4 when everything is binary32 and 16-byte aligned).
 __global__ void gemm_splitk_reduce(const float* __restrict__ ws, long long ldw, int n_stride,
                                    int split_k, int M, int N, float alpha, float beta,
-                                   const float* __restrict__ C, long long ldc, float* __restrict__ D,
-                                   long long ldd, int vec_ok) {
+                                   const void* __restrict__ Cv, long long ldc, void* __restrict__ Dv,
+                                   long long ldd, int vec_ok, int c_f16, int d_f16) {
+    const float* C = static_cast<const float*>(Cv);
+    float* D = static_cast<float*>(Dv);
+    const __half* Ch = static_cast<const __half*>(Cv);
+    __half* Dh = static_cast<__half*>(Dv);
     const long long quads_m = (M + 3) / 4;
     const long long total = quads_m * N;
     for (long long q = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; q < total;
@@ -453,8 +480,9 @@ __global__ void gemm_splitk_reduce(const float* __restrict__ ws, long long ldw, 
                 float acc = 0.f;
                 for (int s = 0; s < split_k; ++s) acc += ws[(n + static_cast<long long>(s) * n_stride) * ldw + m + i];
                 float out = alpha * acc;
-                if (beta != 0.0f) out = fmaf(beta, C[n * ldc + m + i], out);
-                D[n * ldd + m + i] = out;
+                if (beta != 0.0f) out = fmaf(beta, c_f16 ? __half2float(Ch[n * ldc + m + i]) : C[n * ldc + m + i], out);
+                if (d_f16) Dh[n * ldd + m + i] = __float2half_rn(out);
+                else D[n * ldd + m + i] = out;
             }
         }
     }

@@ -37,7 +37,13 @@ struct GemmProblem {
     // panel_flags[j] != 0; panel_k is a multiple of 64
     const unsigned int* panel_flags = nullptr;
     int64_t panel_k = 0;
+    // element types of C and D in memory (B200_F32 by default); when B200_F16, the C / D pointers
+    // above point at binary16 data and ldc / ldd count binary16 elements
+    int c_type = B200_F32;
+    int d_type = B200_F32;
 };
+
+inline int elem_bytes(int type) { return type == B200_F16 ? 2 : 4; }
 
 struct GemmPlan {
     int tile_n;    // 64 / 128 / 256

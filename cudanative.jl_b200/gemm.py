@@ -76,6 +76,16 @@ class Handle:
         _lib.check(_lib.lib().b200_gemm_f16f32(self._h, stream, int(bool(transA)), int(bool(transB)), M, N, K,
                                                float(alpha), a, lda, b, ldb, float(beta), c, ldc, d, ldd), "gemm")
 
+    def gemm_typed(self, transA: bool, transB: bool, M: int, N: int, K: int, alpha: float, A, lda: int, B, ldb: int,
+                   beta: float, Cm, ldc: int, c_type, D, ldd: int, d_type, stream=None) -> None:
+        """``gemm`` with Float16 or Float32 C and D (b200_gemm_f16_typed); types are numpy dtypes."""
+        code = {np.dtype(np.float16): _lib.F16, np.dtype(np.float32): _lib.F32}
+        a, b, d = _addr(A), _addr(B), _addr(D)
+        c = _addr(Cm) if Cm is not None else None
+        _lib.check(_lib.lib().b200_gemm_f16_typed(self._h, stream, int(bool(transA)), int(bool(transB)), M, N, K,
+                                                  float(alpha), a, lda, b, ldb, float(beta), c, ldc, code[np.dtype(c_type)],
+                                                  d, ldd, code[np.dtype(d_type)]), "gemm_typed")
+
     def gemm_gated(self, transA: bool, transB: bool, M: int, N: int, K: int, alpha: float, A, lda: int, B, ldb: int,
                    beta: float, Cm, ldc: int, D, ldd: int, panel_flags, panel_k: int, stream=None) -> None:
         """``gemm`` whose main loop reads columns [j*panel_k, (j+1)*panel_k) of op(A) only once the
@@ -108,6 +118,10 @@ def _addr(x):
     return DevicePtr.of(x).addr
 
 
+def _dtype(x) -> np.dtype:
+    return DevicePtr.of(x).dtype
+
+
 def _dims(x):
     """(rows, cols, ld) of a column-major 2-D operand: CuHostArray, or a torch tensor holding
     the matrix transposed (shape (cols, rows), contiguous), which is how row-major torch stores a
@@ -125,7 +139,8 @@ def gemm_f16f32(handle: Handle, D, A, B, Cm=None, *, alpha: float = 1.0, beta: f
     """``D = alpha*op(A)*op(B) + beta*C`` on column-major device matrices.
 
     Operands are ``CuHostArray`` (shape (rows, cols)) or CUDA tensors whose torch shape is
-    (cols, rows) -- the transposed view of the same column-major memory."""
+    (cols, rows) -- the transposed view of the same column-major memory.  C and D may be Float16 or
+    Float32 independently (the reference's four Config / load_c type combinations); A and B are Float16."""
     ar, ac, lda = _dims(A)
     br, bc, ldb = _dims(B)
     M, K = (ac, ar) if transA else (ar, ac)
@@ -142,8 +157,14 @@ def gemm_f16f32(handle: Handle, D, A, B, Cm=None, *, alpha: float = 1.0, beta: f
             raise ValueError(f"C is {cr}x{cc}, expected {M}x{N}")
     elif beta != 0.0:
         raise ValueError("beta != 0 needs C")
-    handle.gemm(transA, transB, M, N, K, alpha, A, lda, B, ldb, beta if Cm is not None else 0.0, Cm, ldc, D, ldd,
-                stream=stream)
+    c_type = _dtype(Cm) if Cm is not None else np.dtype(np.float32)
+    d_type = _dtype(D)
+    if c_type == np.float32 and d_type == np.float32:
+        handle.gemm(transA, transB, M, N, K, alpha, A, lda, B, ldb, beta if Cm is not None else 0.0, Cm, ldc, D, ldd,
+                    stream=stream)
+    else:
+        handle.gemm_typed(transA, transB, M, N, K, alpha, A, lda, B, ldb, beta if Cm is not None else 0.0, Cm, ldc, c_type,
+                          D, ldd, d_type, stream=stream)
 
 
 # --------------------------------------------------------------------------------------------------

@@ -134,6 +134,18 @@ int b200_gemm_f16f32(b200_handle* h, b200_stream stream, int transA, int transB,
                      int64_t N, int64_t K, float alpha, const void* A, int64_t lda, const void* B,
                      int64_t ldb, float beta, const float* C, int64_t ldc, float* D, int64_t ldd);
 
+/* b200_gemm_f16f32 with the element types of C and D chosen per call (B200_F16 or B200_F32): the
+ * four accumulator / result type combinations WMMA.Config{16,16,16,d_type} and load_c offer
+ * (src/device/cuda/wmma.jl:23-30, :394; all four are swept by test/device/wmma.jl:188-248).
+ * Accumulation is binary32 in every case; a binary16 C is widened when it is read and a binary16
+ * D is rounded once (to nearest even) when it is written.  ldc / ldd count elements of the
+ * respective type.  TMA path: ldc / ldd multiples of 16 bytes, and whole 16-byte chunks of rows
+ * (M % 8 for a binary16 D); the remaining rows run on the simple kernel. */
+int b200_gemm_f16_typed(b200_handle* h, b200_stream stream, int transA, int transB, int64_t M,
+                        int64_t N, int64_t K, float alpha, const void* A, int64_t lda,
+                        const void* B, int64_t ldb, float beta, const void* C, int64_t ldc,
+                        int c_type, void* D, int64_t ldd, int d_type);
+
 /* b200_gemm_f16f32 whose main loop may start before all of A is in this GPU's memory: columns
  * [j*panel_k, (j+1)*panel_k) of op(A) are read only once the 32-bit word panel_flags[j] (device
  * memory) is non-zero.  panel_k is a multiple of 64; at most 32 panels.  The words are meant to

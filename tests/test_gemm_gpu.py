@@ -102,6 +102,20 @@ def test_row_counts_that_are_not_multiples_of_four(handle, oracle, M):
         run_gemm(handle, False, False, 130, N, K, 1.0, padded(a, 136, 0), b, 0.0, None, ldd=136)
 
 
+@pytest.mark.parametrize("K", [100, 101, 65, 7])
+def test_k_tail_is_zero_filled_not_read(handle, oracle, K):
+    """K need not be a multiple of anything: the loads fill elements beyond K with zeros one element at
+    a time, so NaNs sitting in the leading-dimension padding right behind the last k never reach D."""
+    force(handle)
+    M, N = 128, 192
+    for (tA, tB) in LAYOUTS:
+        a, b, c = operands(M, N, K, tA, tB, seed=79)
+        lda = -(-a.shape[0] // 8) * 8 + 8
+        ldb = -(-b.shape[0] // 8) * 8 + 8
+        d = run_gemm(handle, tA, tB, M, N, K, 1.0, padded(a, lda, np.nan), padded(b, ldb, np.nan), 0.0, None)
+        oracle.assert_close(d, oracle.gemm_ref(tA, tB, 1.0, a, b, 0.0, None), f"K={K} tA={tA} tB={tB}")
+
+
 @pytest.mark.parametrize("tile_n", [128, 256])
 def test_pair_many_stage_wraps(handle, oracle, tile_n):
     """2-CTA tiles with a K loop far longer than the stage ring and several tiles per pair."""
@@ -256,6 +270,50 @@ def test_config3_8192_cubed_properties(handle, oracle):
     handle.gemm(True, False, n, n, n, 2.0, a, n, b, n, 0.0, None, n, d, n)
     handle.gemm(True, False, n, n, n, 4.0, a, n, b, n, 0.0, None, n, d2, n)
     assert np.array_equal(Array(d2), np.float32(2.0) * Array(d))
+
+
+@pytest.mark.parametrize("c_type,d_type", [(np.float16, np.float16), (np.float16, np.float32), (np.float32, np.float16)])
+@pytest.mark.parametrize("kernel,split_k", [(_lib.KERNEL_TCGEN05, 0), (_lib.KERNEL_TCGEN05, 3), (_lib.KERNEL_SIMPLE, 0)])
+def test_float16_c_and_d(handle, oracle, c_type, d_type, kernel, split_k):
+    """The reference's other three accumulator / result type combinations (wmma.jl:23-30; swept by
+    test/device/wmma.jl:188-248) on whole matrices: Float16 C is widened on load, Float16 D rounded once."""
+    from cudanative_jl_b200.gemm import gemm_f16f32
+    force(handle, kernel, split_k=split_k)
+    M, N, K = 392, 264, 520
+    for (tA, tB) in LAYOUTS:
+        a, b, c32 = operands(M, N, K, tA, tB, seed=88)
+        c = c32.astype(c_type)
+        d_dev = CuArray(np.full((M, N), -3.0, dtype=d_type, order="F"))
+        gemm_f16f32(handle, d_dev, CuArray(a), CuArray(b), CuArray(c), alpha=1.5, beta=0.5, transA=tA, transB=tB)
+        d = Array(d_dev)
+        assert handle.device_status()[0] == 0 and d.dtype == d_type
+        ref = oracle.gemm_ref(tA, tB, 1.5, a, b, 0.5, c.astype(np.float32))
+        if d_type == np.float16:  # one rounding to nearest even on the way out, nothing more
+            assert np.max(np.abs(d.astype(np.float32) - ref.astype(np.float16).astype(np.float32))
+                          / (np.abs(ref) + 1)) <= 2.0 ** -10
+        oracle.assert_close(d.astype(np.float32), ref, f"C {c_type.__name__} D {d_type.__name__} tA={tA} tB={tB}")
+    assert handle.last_launch()["kernel"] == kernel
+    # beta == 0 with a Float16 D and no C
+    a, b, _ = operands(M, N, K, False, False, seed=89)
+    d_dev = CuArray(np.zeros((M, N), dtype=np.float16, order="F"))
+    gemm_f16f32(handle, d_dev, CuArray(a), CuArray(b), alpha=1.0)
+    oracle.assert_close(Array(d_dev).astype(np.float32), oracle.gemm_ref(False, False, 1.0, a, b, 0.0, None), "f16 D, no C")
+
+
+def test_float16_d_with_ragged_rows(handle, oracle):
+    """Float16 D: 16-byte store chunks hold 8 rows; M % 8 rows go to the plain kernel and the rows
+    below M stay untouched."""
+    force(handle, _lib.KERNEL_AUTO)
+    M, N, K, ld = 267, 136, 128, 280
+    a, b, c32 = operands(M, N, K, False, False, seed=90)
+    c = padded(c32.astype(np.float16), ld, 0)
+    d_dev = CuArray(np.full((ld, N), 7.5, dtype=np.float16, order="F"))
+    handle.gemm_typed(False, False, M, N, K, 1.0, CuArray(padded(a, 272, 0)), 272, CuArray(b), K, 1.0, CuArray(c), ld, np.float16,
+                      d_dev, ld, np.float16)
+    d = Array(d_dev)
+    oracle.assert_close(d[:M].astype(np.float32), oracle.gemm_ref(False, False, 1.0, a, b, 1.0, c32.astype(np.float16).astype(np.float32)),
+                        "ragged f16 D")
+    assert np.all(d[M:] == np.float16(7.5))
 
 
 def _streams(lib, n):
