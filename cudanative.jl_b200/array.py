@@ -73,7 +73,15 @@ class CuHostArray:
             self.shape = tuple(shape)
         self.nbytes = int(np.prod(self.shape, dtype=np.int64)) * self.dtype.itemsize
         p = C.c_void_p()
-        _lib.check(L.b200_malloc(C.byref(p), self.nbytes), "CuHostArray")
+        status = L.b200_malloc(C.byref(p), self.nbytes)
+        if status == _lib.CUDA_ERROR and b"cudaErrorMemoryAllocation" in L.b200_last_error():
+            # out of memory: let unreachable arrays release their device memory and try once more,
+            # as the reference does (src/array.jl:23-29: Mem.alloc, on OOM GC.gc(), retry)
+            import gc
+
+            gc.collect()
+            status = L.b200_malloc(C.byref(p), self.nbytes)
+        _lib.check(status, "CuHostArray")
         self.ptr = p.value
         if host is not None and self.nbytes:
             _lib.check(L.b200_memcpy_h2d(self.ptr, host.ctypes.data, self.nbytes, None), "upload")

@@ -69,3 +69,36 @@ def test_invalid_layout_and_type_messages():
     with pytest.raises(ValueError, match="Invalid type float32 for matrix a"):
         wmma._frag_elems("a", np.float32)  # wmma.jl:469-476
     assert wmma._frag_elems("a", np.float16) == 16 and wmma._frag_elems("c", np.float32) == 8  # wmma.jl:413-420
+
+
+def test_cuhostarray_retries_allocation_after_gc(monkeypatch, pkg):
+    """src/array.jl:23-29: an allocation that fails for lack of memory is retried once after a
+    garbage collection.  Exercised against a stand-in for the library (no GPU needed)."""
+    import ctypes as C
+    from cudanative_jl_b200 import _lib, array
+
+    calls = {"malloc": 0, "gc": 0}
+
+    class FakeLib:
+        def b200_malloc(self, out, nbytes):
+            calls["malloc"] += 1
+            if calls["malloc"] == 1:
+                return _lib.CUDA_ERROR
+            C.cast(out, C.POINTER(C.c_void_p))[0] = 4096
+            return _lib.OK
+
+        def b200_last_error(self):
+            return b"cudaMalloc(dptr, bytes ? bytes : 1): cudaErrorMemoryAllocation (out of memory)"
+
+        def b200_status_string(self, s):
+            return b"B200_CUDA_ERROR"
+
+        def b200_free(self, p):
+            return _lib.OK
+
+    import gc
+    monkeypatch.setattr(_lib, "lib", lambda: FakeLib())
+    monkeypatch.setattr(gc, "collect", lambda *a: calls.__setitem__("gc", calls["gc"] + 1) or 0)
+    arr = array.CuHostArray(np.float32, shape=(16, 16))
+    assert arr.ptr == 4096 and calls == {"malloc": 2, "gc": 1}
+    arr.ptr = None  # nothing real to free
