@@ -229,6 +229,21 @@ def launch_groups(n_panels: int, first: int = 1, growth: float = 2.5) -> list[tu
     return out
 
 
+def subblock_cols(panels: list[tuple[int, int]], world: int) -> list[list[tuple[int, int]]]:
+    """For every K panel [k0, k1) the column range of A each rank owns during the transfer:
+    ``out[p][g] = (c0, c1)``.  A panel is cut into world - 1 sub-blocks, one per receiving rank, so
+    that rank 0 sends every byte of A exactly once (its link is the bottleneck of the scatter) and
+    forwards nothing; rank 0's own range is empty."""
+    out = []
+    for (k0, k1) in panels:
+        row = [(k0, k0)]
+        for g in range(1, world):
+            c0, c1 = slab_bounds(k1 - k0, world - 1, g - 1, align=8)
+            row.append((k0 + c0, k0 + c1))
+        out.append(row)
+    return out
+
+
 class ShardedGemm:
     """``D[:, slab_r] = alpha * A * B[:, slab_r] + beta * C[:, slab_r]`` on every rank r.
 
@@ -356,14 +371,7 @@ class ShardedGemm:
         G, P = self.world, len(self.panels)
         self._a_table = (C.c_void_p * G)(*[self._raw.ptr if g == self.rank else self._peers[g] for g in range(G)])
         self._flag_table = (C.c_void_p * G)(*[self._raw_flags.ptr if g == self.rank else self._peer_flags[g] for g in range(G)])
-        # A panel is cut into G - 1 sub-blocks, one per receiving rank: rank 0 then sends every byte
-        # of A exactly once (its link is the bottleneck of the scatter) and forwards nothing.
-        cols = []
-        for (k0, k1) in self.panels:
-            cols += [k0, k0]  # rank 0 owns no sub-block
-            for g in range(1, G):
-                c0, c1 = slab_bounds(k1 - k0, G - 1, g - 1, align=8)
-                cols += [k0 + c0, k0 + c1]
+        cols = [c for panel in subblock_cols(self.panels, G) for rng_ in panel for c in rng_]
         self._sub_cols = (C.c_int64 * (2 * G * P))(*cols)
         return self.A
 

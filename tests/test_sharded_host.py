@@ -7,7 +7,7 @@ from pathlib import Path
 
 import pytest
 
-from cudanative_jl_b200.gemm import launch_groups, panel_bounds, slab_bounds
+from cudanative_jl_b200.gemm import launch_groups, panel_bounds, slab_bounds, subblock_cols
 
 ROOT = Path(__file__).resolve().parent.parent
 
@@ -40,6 +40,23 @@ def test_launch_groups_cover_the_panels_and_grow(n):
     assert all(a1 == b0 and a1 > a0 for (a0, a1), (b0, _) in zip(g, g[1:]))
     sizes = [b - a for (a, b) in g]
     assert sizes[0] == 1 and sizes == sorted(sizes) and len(g) <= 5
+
+
+@pytest.mark.parametrize("world", [2, 3, 4, 8])
+@pytest.mark.parametrize("k,panel_k", [(16384, 1024), (200, 64), (1000, 320)])
+def test_transfer_subblocks_tile_every_panel(world, k, panel_k):
+    """Scatter / all-gather ownership: within each panel the receiving ranks' column ranges are
+    disjoint, contiguous and cover the panel; rank 0 owns nothing (it only sends)."""
+    panels = [(k0, min(k, k0 + panel_k)) for k0 in range(0, k, panel_k)]
+    sub = subblock_cols(panels, world)
+    assert len(sub) == len(panels)
+    for (k0, k1), row in zip(panels, sub):
+        assert len(row) == world and row[0] == (k0, k0)
+        edge = k0
+        for (c0, c1) in row[1:]:
+            assert c0 == edge and c1 >= c0
+            edge = c1
+        assert edge == k1
 
 
 @pytest.mark.parametrize("world,shape", [(2, (96, 640, 200)), (3, (64, 512, 130))])
