@@ -42,6 +42,29 @@ def test_ptx_exports_the_52_reference_names(pkg):
     assert ".target sm_100a" in text
 
 
+def _ptx_body(text, name):
+    i = text.index(name + "(")
+    return text[i:text.index("\n}\n", i)]
+
+
+@pytest.mark.parametrize("ty", ["f16", "f32"])
+@pytest.mark.parametrize("lay", ["col", "row"])
+def test_ptx_uses_the_address_space_of_the_variant(pkg, lay, ty):
+    """test/device/wmma.jl:254-291 checks that stores through a global / shared pointer compile to the
+    state-space forms of the instruction, not the generic one.  Same property here: the _global and
+    _shared variants load and store with ld/st.global and ld/st.shared, the unsuffixed ones generically."""
+    pkg.build.build_device_lib()
+    text = PTX.read_text()
+    mem = lambda body: set(re.findall(r"\b(?:st|ld)\.(global|shared)\.", body))
+    generic = lambda body: re.search(r"\b(?:st|ld)\.(?:b16|u16|f32|b32|u32)\b", body) is not None
+    for op, mat in (("store_d", ""), ("load_c", "")):
+        base = f"b200_wmma_{op}_{lay}_m16n16k16"
+        assert mem(_ptx_body(text, f"{base}_global_stride_{ty}")) == {"global"}
+        assert mem(_ptx_body(text, f"{base}_shared_stride_{ty}")) == {"shared"}
+        body = _ptx_body(text, f"{base}_stride_{ty}")
+        assert mem(body) == set() and generic(body)
+
+
 @pytest.fixture(scope="module")
 def harness(pkg):
     pkg.build.build_device_lib()
