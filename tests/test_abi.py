@@ -55,3 +55,19 @@ def test_no_device_is_reported_not_hidden(lib, pkg):
     rc = lib.b200_create(C.byref(h), 0)
     assert rc in (pkg._lib.NO_DEVICE, pkg._lib.CUDA_ERROR)
     assert h.value is None
+
+
+def test_header_is_plain_c(tmp_path):
+    """The ABI header must compile as C (it is what a Julia / Go / Rust FFI generator would read)."""
+    import shutil
+    import subprocess
+
+    gcc = shutil.which("gcc") or shutil.which("cc")
+    if gcc is None:
+        import pytest
+        pytest.skip("no C compiler")
+    src = tmp_path / "use.c"
+    src.write_text('#include "b200wmma.h"\nint main(void) { b200_handle* h = 0; return b200_destroy(h) == B200_OK ? 0 : 1; }\n')
+    r = subprocess.run([gcc, "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-I", str(HEADER.parent), "-c", str(src),
+                        "-o", str(tmp_path / "use.o")], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
