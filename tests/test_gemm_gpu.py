@@ -163,6 +163,19 @@ def test_split_k(handle, oracle, split_k):
     assert handle.last_launch()["split_k"] == {2: 2, 3: 3, 8: 7}[split_k]
 
 
+@pytest.mark.parametrize("tA,tB", LAYOUTS)
+def test_split_k_with_two_cta_tiles(handle, oracle, tA, tB):
+    """k-slices on 2-CTA 256-wide tiles, ragged in every dimension, several tiles per cluster."""
+    force(handle, tile_n=256, pair=2, split_k=4, max_ctas=8)
+    M, N, K = 520, 600, 1100
+    a, b, c = operands(M, N, K, tA, tB, seed=72)
+    lda, ldb = -(-a.shape[0] // 8) * 8, -(-b.shape[0] // 8) * 8
+    d = run_gemm(handle, tA, tB, M, N, K, 0.5, padded(a, lda, 0), padded(b, ldb, 0), 1.5, c)
+    oracle.assert_close(d, oracle.gemm_ref(tA, tB, 0.5, a, b, 1.5, c), f"pair split-K tA={tA} tB={tB}")
+    info = handle.last_launch()
+    assert info["split_k"] == 4 and info["cta_pair"] == 2
+
+
 def test_unaligned_and_empty_shapes_take_the_simple_kernel(handle, oracle):
     force(handle, _lib.KERNEL_AUTO)
     # lda = 45 is not a multiple of 8: TMA cannot address it
