@@ -13,7 +13,7 @@ LIB_PATH = Path(__file__).resolve().parent / "libb200wmma.so"
 
 OK, INVALID_ARG, UNSUPPORTED, CUDA_ERROR, DEVICE_TIMEOUT, NO_DEVICE = range(6)
 COL_MAJOR, ROW_MAJOR = 0, 1
-F16, F32 = 0, 1
+F16, F32, BF16 = 0, 1, 2
 MATRIX_A, MATRIX_B, ACCUMULATOR = 0, 1, 2
 LOWER_WARP, LOWER_TCGEN05 = 0, 1
 KERNEL_AUTO, KERNEL_TCGEN05, KERNEL_SIMPLE = 0, 1, 2
@@ -39,6 +39,9 @@ SIGNATURES = {
     "b200_last_launch": (_i, [_p, _ip, _ip, _ip, _ip, _ip]),
     "b200_gemm_f16f32": (_i, [_p, _p, _i, _i, _i64, _i64, _i64, _f, _p, _i64, _p, _i64, _f, _p, _i64, _p, _i64]),
     "b200_gemm_f16_typed": (_i, [_p, _p, _i, _i, _i64, _i64, _i64, _f, _p, _i64, _p, _i64, _f, _p, _i64, _i, _p, _i64, _i]),
+    "b200_gemm_ex": (_i, [_p, _p, _i, _i, _i64, _i64, _i64, _f, _p, _i64, _p, _i64, _i, _f, _p, _i64, _i, _p, _i64, _i]),
+    "b200_gemm_strided_batched": (_i, [_p, _p, _i, _i, _i64, _i64, _i64, _f, _p, _i64, _i64, _p, _i64, _i64, _i, _f, _p, _i64,
+                                       _i64, _i, _p, _i64, _i64, _i, _i64]),
     "b200_gemm_f16f32_gated": (_i, [_p, _p, _i, _i, _i64, _i64, _i64, _f, _p, _i64, _p, _i64, _f, _p, _i64, _p, _i64, _p, _i64]),
     "b200_stream_write_u32": (_i, [_p, _p, C.c_uint32]),
     "b200_stream_wait_u32": (_i, [_p, _p, C.c_uint32]),
@@ -68,6 +71,7 @@ SIGNATURES = {
     "b200_stream_destroy": (_i, [_p]),
     "b200_fill_f16": (_i, [_p, _p, _i64, _i64, _i64, _u64, _u64, _u64, _i, _f]),
     "b200_fill_f32": (_i, [_p, _p, _i64, _i64, _i64, _u64, _u64, _u64, _i, _f]),
+    "b200_fill_bf16": (_i, [_p, _p, _i64, _i64, _i64, _u64, _u64, _u64, _i, _f]),
 }
 
 

@@ -88,6 +88,12 @@ int validate(const GemmProblem& g) {
     if (g.lda < std::max<int64_t>(1, a_rows)) return fail(B200_INVALID_ARG, "gemm: lda smaller than the rows of stored A");
     if (g.ldb < std::max<int64_t>(1, b_rows)) return fail(B200_INVALID_ARG, "gemm: ldb smaller than the rows of stored B");
     if (g.ldd < std::max<int64_t>(1, g.M)) return fail(B200_INVALID_ARG, "gemm: ldd smaller than M");
+    if (g.batch < 0) return fail(B200_INVALID_ARG, "gemm: negative batch count");
+    if (g.batch > 1) {
+        if (g.stride_a < 0 || g.stride_b < 0 || g.stride_c < 0 || g.stride_d < 0)
+            return fail(B200_INVALID_ARG, "gemm: negative batch stride");
+        if (g.stride_d < g.ldd * g.N) return fail(B200_INVALID_ARG, "gemm: stride_d smaller than one D matrix (results would overlap)");
+    }
     if (g.beta != 0.0f && g.ldc < std::max<int64_t>(1, g.M)) return fail(B200_INVALID_ARG, "gemm: ldc smaller than M");
     if (g.M > 0 && g.N > 0) {
         if (!g.D) return fail(B200_INVALID_ARG, "gemm: D is null");
@@ -121,7 +127,7 @@ GemmPlan make_plan(const b200_handle* h, const GemmProblem& g) {
 int run_gemm(b200_handle* h, cudaStream_t stream, const GemmProblem& g) {
     int rc = validate(g);
     if (rc) return rc;
-    if (g.M == 0 || g.N == 0) return B200_OK;
+    if (g.M == 0 || g.N == 0 || g.batch == 0) return B200_OK;
     std::string why;
     const bool eligible = gemm_tcgen05_eligible(g, &why);
     int kernel = h->force_kernel;
@@ -139,6 +145,28 @@ int run_gemm(b200_handle* h, cudaStream_t stream, const GemmProblem& g) {
             strip.D = reinterpret_cast<float*>(reinterpret_cast<char*>(g.D) + skip * elem_bytes(g.d_type));
             if ((rc = gemm_simple_launch(strip, stream, nullptr))) return rc;
             return run_gemm(h, stream, top);
+        }
+    }
+    if (kernel == B200_KERNEL_AUTO && !eligible && g.batch > 1) {
+        // The batch cannot run as one TMA launch (strides).  If a single matrix can, multiply them one
+        // launch each; otherwise all of them go to the plain kernel in one launch.
+        GemmProblem one = g;
+        one.batch = 1;
+        bool one_ok = gemm_tcgen05_eligible(one, nullptr);
+        if (!one_ok && (g.M % m_quant) && g.M > m_quant) {
+            one.M = g.M - g.M % m_quant;
+            one_ok = gemm_tcgen05_eligible(one, nullptr);
+            one.M = g.M;
+        }
+        if (one_ok) {
+            for (int64_t i = 0; i < g.batch; ++i) {
+                one.A = static_cast<const char*>(g.A) + 2 * i * g.stride_a;
+                one.B = static_cast<const char*>(g.B) + 2 * i * g.stride_b;
+                if (g.C) one.C = reinterpret_cast<const float*>(reinterpret_cast<const char*>(g.C) + i * g.stride_c * elem_bytes(g.c_type));
+                one.D = reinterpret_cast<float*>(reinterpret_cast<char*>(g.D) + i * g.stride_d * elem_bytes(g.d_type));
+                if ((rc = run_gemm(h, stream, one))) return rc;
+            }
+            return B200_OK;
         }
     }
     if (kernel == B200_KERNEL_AUTO) kernel = eligible ? B200_KERNEL_TCGEN05 : B200_KERNEL_SIMPLE;
@@ -341,6 +369,40 @@ int b200_gemm_f16_typed(b200_handle* h, b200_stream stream, int transA, int tran
     g.c_type = c_type;
     g.d_type = d_type;
     return run_gemm(h, static_cast<cudaStream_t>(stream), g);
+}
+
+namespace {
+bool is_elem_type(int t) { return t == B200_F16 || t == B200_F32 || t == B200_BF16; }
+}  // namespace
+
+int b200_gemm_strided_batched(b200_handle* h, b200_stream stream, int transA, int transB, int64_t M, int64_t N,
+                              int64_t K, float alpha, const void* A, int64_t lda, int64_t stride_a, const void* B,
+                              int64_t ldb, int64_t stride_b, int ab_type, float beta, const void* C, int64_t ldc,
+                              int64_t stride_c, int c_type, void* D, int64_t ldd, int64_t stride_d, int d_type,
+                              int64_t batch) {
+    if (!h) return fail(B200_INVALID_ARG, "null handle");
+    if (ab_type != B200_F16 && ab_type != B200_BF16)
+        return fail(B200_INVALID_ARG, "invalid element type: A and B must be Float16 or bfloat16");
+    if (!is_elem_type(c_type) || !is_elem_type(d_type))
+        return fail(B200_INVALID_ARG, "invalid element type: C and D must be Float16, bfloat16 or Float32");
+    GemmProblem g{transA, transB, M, N, K, alpha, beta, A, lda, B, ldb, static_cast<const float*>(C), ldc,
+                  static_cast<float*>(D), ldd};
+    g.c_type = c_type;
+    g.d_type = d_type;
+    g.ab_type = ab_type;
+    g.batch = batch;
+    g.stride_a = stride_a;
+    g.stride_b = stride_b;
+    g.stride_c = stride_c;
+    g.stride_d = stride_d;
+    return run_gemm(h, static_cast<cudaStream_t>(stream), g);
+}
+
+int b200_gemm_ex(b200_handle* h, b200_stream stream, int transA, int transB, int64_t M, int64_t N, int64_t K,
+                 float alpha, const void* A, int64_t lda, const void* B, int64_t ldb, int ab_type, float beta,
+                 const void* C, int64_t ldc, int c_type, void* D, int64_t ldd, int d_type) {
+    return b200_gemm_strided_batched(h, stream, transA, transB, M, N, K, alpha, A, lda, 0, B, ldb, 0, ab_type, beta, C,
+                                     ldc, 0, c_type, D, ldd, 0, d_type, 1);
 }
 
 int b200_gemm_f16f32_gated(b200_handle* h, b200_stream stream, int transA, int transB, int64_t M, int64_t N, int64_t K,

@@ -3,8 +3,9 @@
 // The simple kernel takes any shape, leading dimension and alignment, so it backs the shapes the
 // TMA path cannot address (unaligned pointers, K == 0) and serves as an independent on-device
 // check of the tcgen05 kernel at sizes a CPU product would take minutes for.  Products of two
-// binary16 values are exact in binary32, so it differs from the tensor-core result only in the
-// order of the FP32 additions.
+// binary16 (or bfloat16) values are exact in binary32, so it differs from the tensor-core result
+// only in the order of the FP32 additions.  Batched problems put the matrix index in blockIdx.z.
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
 #include "internal.h"
@@ -16,15 +17,31 @@ namespace {
 constexpr int kTile = 64;   // output tile per block
 constexpr int kTileK = 16;  // k per shared-memory step
 
+struct SimpleBatch {
+    int64_t count, stride_a, stride_b, stride_c, stride_d;  // strides in elements
+};
+
+// 16-bit storage -> binary32: bfloat16 is the upper half of a binary32
+__device__ __forceinline__ float widen16(unsigned short raw, int bf16) {
+    return bf16 ? __uint_as_float(static_cast<uint32_t>(raw) << 16) : __half2float(__ushort_as_half(raw));
+}
+
 template <bool kTransA, bool kTransB>
 __global__ void __launch_bounds__(256)
-gemm_simple_kernel(int64_t M, int64_t N, int64_t K, float alpha, const __half* __restrict__ A, int64_t lda,
-                   const __half* __restrict__ B, int64_t ldb, float beta, const void* Cv, int64_t ldc, void* Dv,
-                   int64_t ldd, int c_f16, int d_f16) {
+gemm_simple_kernel(int64_t M, int64_t N, int64_t K, float alpha, const unsigned short* __restrict__ A0, int64_t lda,
+                   const unsigned short* __restrict__ B0, int64_t ldb, float beta, const void* Cv0, int64_t ldc,
+                   void* Dv0, int64_t ldd, int ab_bf16, int c_fmt, int d_fmt, SimpleBatch batch) {
+  for (int64_t bz = blockIdx.z; bz < batch.count; bz += gridDim.z) {
+    const unsigned short* A = A0 + bz * batch.stride_a;
+    const unsigned short* B = B0 + bz * batch.stride_b;
+    const int c_bytes = c_fmt == 0 ? 4 : 2, d_bytes = d_fmt == 0 ? 4 : 2;
+    const void* Cv = static_cast<const char*>(Cv0) + bz * batch.stride_c * c_bytes;
+    void* Dv = static_cast<char*>(Dv0) + bz * batch.stride_d * d_bytes;
     const float* C = static_cast<const float*>(Cv);
     float* D = static_cast<float*>(Dv);
-    const __half* Ch = static_cast<const __half*>(Cv);
+    const unsigned short* Ch = static_cast<const unsigned short*>(Cv);
     __half* Dh = static_cast<__half*>(Dv);
+    __nv_bfloat16* Db = static_cast<__nv_bfloat16*>(Dv);
     __shared__ float sA[kTileK][kTile + 1];
     __shared__ float sB[kTileK][kTile + 1];
     const int tx = threadIdx.x & 15;  // 4 rows each
@@ -38,7 +55,7 @@ gemm_simple_kernel(int64_t M, int64_t N, int64_t K, float alpha, const __half* _
             if (kTransA) { kk = e % kTileK; mm = e / kTileK; } else { mm = e % kTile; kk = e / kTile; }
             const int64_t m = m0 + mm, k = k0 + kk;
             float v = 0.f;
-            if (m < M && k < K) v = __half2float(kTransA ? A[k + m * lda] : A[m + k * lda]);
+            if (m < M && k < K) v = widen16(kTransA ? A[k + m * lda] : A[m + k * lda], ab_bf16);
             sA[kk][mm] = v;
         }
         for (int e = threadIdx.x; e < kTile * kTileK; e += 256) {
@@ -46,7 +63,7 @@ gemm_simple_kernel(int64_t M, int64_t N, int64_t K, float alpha, const __half* _
             if (kTransB) { nn = e % kTile; kk = e / kTile; } else { kk = e % kTileK; nn = e / kTileK; }
             const int64_t n = n0 + nn, k = k0 + kk;
             float v = 0.f;
-            if (n < N && k < K) v = __half2float(kTransB ? B[n + k * ldb] : B[k + n * ldb]);
+            if (n < N && k < K) v = widen16(kTransB ? B[n + k * ldb] : B[k + n * ldb], ab_bf16);
             sB[kk][nn] = v;
         }
         __syncthreads();
@@ -73,11 +90,14 @@ gemm_simple_kernel(int64_t M, int64_t N, int64_t K, float alpha, const __half* _
             const int64_t m = m0 + tx * 4 + i;
             if (m >= M) continue;
             float v = alpha * acc[i][j];
-            if (beta != 0.0f) v = fmaf(beta, c_f16 ? __half2float(Ch[m + n * ldc]) : C[m + n * ldc], v);
-            if (d_f16) Dh[m + n * ldd] = __float2half_rn(v);
+            if (beta != 0.0f) v = fmaf(beta, c_fmt ? widen16(Ch[m + n * ldc], c_fmt == 2) : C[m + n * ldc], v);
+            if (d_fmt == 2) Db[m + n * ldd] = __float2bfloat16_rn(v);
+            else if (d_fmt == 1) Dh[m + n * ldd] = __float2half_rn(v);
             else D[m + n * ldd] = v;
         }
     }
+    __syncthreads();  // the shared tiles are reused by the next matrix of the batch
+  }
 }
 
 template <typename T>
@@ -88,8 +108,8 @@ __global__ void fill_kernel(T* out, int64_t rows, int64_t cols, int64_t ld, uint
          idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
         const int64_t j = idx / rows, i = idx - j * rows;
         const float v = synth_value(seed, matrix_id, index0 + static_cast<uint64_t>(idx), dist) * scale;
-        if constexpr (sizeof(T) == 2) out[i + j * ld] = __float2half_rn(v);
-        else out[i + j * ld] = v;
+        if constexpr (sizeof(T) == 4) out[i + j * ld] = v;
+        else out[i + j * ld] = T(v);  // __half and __nv_bfloat16 convert with round-to-nearest-even
     }
 }
 
@@ -113,12 +133,14 @@ int gemm_simple_launch(const GemmProblem& g, cudaStream_t stream, LaunchInfo* in
     if (g.M == 0 || g.N == 0) return B200_OK;
     const int64_t gx = (g.M + kTile - 1) / kTile, gy = (g.N + kTile - 1) / kTile;
     if (gy > 65535) return fail(B200_UNSUPPORTED, "simple kernel: N too large for one launch");
-    dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(gy));
-    const __half* A = static_cast<const __half*>(g.A);
-    const __half* B = static_cast<const __half*>(g.B);
+    const int64_t count = g.batch > 1 ? g.batch : 1;
+    dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(gy), static_cast<unsigned>(count < 1024 ? count : 1024));
+    const unsigned short* A = static_cast<const unsigned short*>(g.A);
+    const unsigned short* B = static_cast<const unsigned short*>(g.B);
+    const SimpleBatch batch = {count, g.stride_a, g.stride_b, g.stride_c, g.stride_d};
 #define B200_SIMPLE(TA, TB) \
     gemm_simple_kernel<TA, TB><<<grid, 256, 0, stream>>>(g.M, g.N, g.K, g.alpha, A, g.lda, B, g.ldb, g.beta, g.C, g.ldc, g.D, g.ldd, \
-                                                         g.c_type == B200_F16 ? 1 : 0, g.d_type == B200_F16 ? 1 : 0)
+                                                         g.ab_type == B200_BF16 ? 1 : 0, elem_fmt(g.c_type), elem_fmt(g.d_type), batch)
     if (g.transA) { if (g.transB) B200_SIMPLE(true, true); else B200_SIMPLE(true, false); }
     else          { if (g.transB) B200_SIMPLE(false, true); else B200_SIMPLE(false, false); }
 #undef B200_SIMPLE
@@ -127,7 +149,7 @@ int gemm_simple_launch(const GemmProblem& g, cudaStream_t stream, LaunchInfo* in
         info->kernel = B200_KERNEL_SIMPLE;
         info->tile_n = kTile;
         info->split_k = 1;
-        info->ctas = static_cast<int>(gx * gy);
+        info->ctas = static_cast<int>(gx * gy * grid.z);
         info->cta_pair = 1;
     }
     return B200_OK;
@@ -145,4 +167,10 @@ extern "C" int b200_fill_f32(b200_stream stream, float* dptr, int64_t rows, int6
                              uint64_t matrix_id, uint64_t index0, int dist, float scale) {
     return b200::fill_launch<float>(static_cast<cudaStream_t>(stream), dptr, rows, cols, ld, seed, matrix_id, index0,
                                     dist, scale);
+}
+
+extern "C" int b200_fill_bf16(b200_stream stream, void* dptr, int64_t rows, int64_t cols, int64_t ld, uint64_t seed,
+                              uint64_t matrix_id, uint64_t index0, int dist, float scale) {
+    return b200::fill_launch<__nv_bfloat16>(static_cast<cudaStream_t>(stream), static_cast<__nv_bfloat16*>(dptr), rows,
+                                            cols, ld, seed, matrix_id, index0, dist, scale);
 }

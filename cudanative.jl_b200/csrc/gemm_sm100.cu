@@ -27,18 +27,26 @@ EncodeFn get_encode_fn() {
     return fn;
 }
 
-// 2-D tensor map over a column-major matrix: dim0 (contiguous) has `inner` elements, dim1 has
-// `outer` elements `ld` elements apart.
+// Matrices of one launch: how many and how far apart (elements); count == 0 asks for a 2-D map.
+struct BatchDim {
+    int64_t count = 0;
+    int64_t stride = 0;
+};
+
+// Tensor map over a column-major matrix: dim0 (contiguous) has `inner` elements, dim1 has `outer`
+// elements `ld` elements apart; batched problems add dim2 = matrix of the batch (box extent 1).
 int make_map_2d(CUtensorMap* tm, CUtensorMapDataType dt, int elem_bytes, const void* base, int64_t inner,
                 int64_t outer, int64_t ld, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle sw,
-                const char* what) {
+                const char* what, BatchDim batch = BatchDim()) {
     EncodeFn enc = get_encode_fn();
     if (!enc) return fail(B200_CUDA_ERROR, "cuTensorMapEncodeTiled entry point not found");
-    cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
-    cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * elem_bytes};
-    cuuint32_t box[2] = {box_inner, box_outer};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = enc(tm, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+    cuuint64_t dims[3] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer),
+                          static_cast<cuuint64_t>(batch.count)};
+    cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld) * elem_bytes, static_cast<cuuint64_t>(batch.stride) * elem_bytes};
+    cuuint32_t box[3] = {box_inner, box_outer, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(tm, dt, batch.count > 0 ? 3 : 2, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE,
                      sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
         return fail(B200_CUDA_ERROR, std::string("cuTensorMapEncodeTiled failed for ") + what + " (CUresult " +
@@ -46,11 +54,11 @@ int make_map_2d(CUtensorMap* tm, CUtensorMapDataType dt, int elem_bytes, const v
     return B200_OK;
 }
 
-template <int kBN, bool kAMn, bool kBMn, int kCtas>
-int launch_one(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const CUtensorMap& tmD,
-               const GemmParams& p, int grid, cudaStream_t stream) {
+template <int kBN, bool kAMn, bool kBMn, int kCtas, bool kBatch>
+int launch_kernel(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const CUtensorMap& tmD,
+                  const GemmParams& p, int grid, cudaStream_t stream) {
     using Cfg = GemmCfg<kBN, kAMn, kBMn, kCtas>;
-    auto kern = gemm_f16f32_tcgen05<kBN, kAMn, kBMn, kCtas>;
+    auto kern = gemm_f16f32_tcgen05<kBN, kAMn, kBMn, kCtas, kBatch>;
     // per device and per function; cheap enough to repeat on every launch
     B200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
     cudaLaunchConfig_t cfg = {};
@@ -67,6 +75,13 @@ int launch_one(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap
     cfg.numAttrs = 1;
     B200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmC, tmD, p));
     return B200_OK;
+}
+
+template <int kBN, bool kAMn, bool kBMn, int kCtas>
+int launch_one(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const CUtensorMap& tmD,
+               const GemmParams& p, int grid, cudaStream_t stream) {
+    if (p.batch > 1) return launch_kernel<kBN, kAMn, kBMn, kCtas, true>(tmA, tmB, tmC, tmD, p, grid, stream);
+    return launch_kernel<kBN, kAMn, kBMn, kCtas, false>(tmA, tmB, tmC, tmD, p, grid, stream);
 }
 
 template <int kBN, int kCtas>
@@ -94,7 +109,7 @@ Geometry geometry(const GemmProblem& g, const GemmPlan& plan) {
     q.tiles_m = static_cast<int>((g.M + tile_m - 1) / tile_m);
     q.tiles_n = static_cast<int>((g.N + plan.tile_n - 1) / plan.tile_n);
     q.kb_total = static_cast<int>((g.K + 63) / 64);
-    int s = plan.split_k < 1 ? 1 : plan.split_k;
+    int s = (plan.split_k < 1 || g.batch > 1) ? 1 : plan.split_k;  // a batch already is parallel work
     if (s > q.kb_total) s = q.kb_total;
     q.kb_per_split = (q.kb_total + s - 1) / s;
     q.split_k = (q.kb_total + q.kb_per_split - 1) / q.kb_per_split;  // no empty slices
@@ -127,8 +142,20 @@ bool gemm_tcgen05_eligible(const GemmProblem& g, std::string* why) {
         return no("ldc and ldd must be multiples of 16 bytes for TMA");
     // bulk tensor stores clip at 16-byte granularity: with a ragged last chunk every column
     // would spill into the rows M .. roundup(M) - 1 of the caller's buffer
-    if (g.M % d_quant) return no(g.d_type == B200_F16 ? "M must be a multiple of 8 for Float16 D (bulk stores are 16-byte granular)"
-                                                      : "M must be a multiple of 4 (bulk stores are 16-byte granular)");
+    if (g.M % d_quant) return no(d_quant == 8 ? "M must be a multiple of 8 for 16-bit D (bulk stores are 16-byte granular)"
+                                              : "M must be a multiple of 4 (bulk stores are 16-byte granular)");
+    if (g.batch > 1) {
+        // the matrix index becomes a third tensor-map dimension: its stride obeys the same 16-byte
+        // rule as a leading dimension, and matrices must not overlap (or repeat: stride 0)
+        if (g.panel_flags) return no("gated A is not available for batches");
+        if (g.batch * ((g.M + 127) / 128) * ((g.N + 63) / 64) > 0x7fffff00ll) return no("too many tiles for one launch");
+        const int64_t a_cols = g.transA ? g.M : g.K, b_cols = g.transB ? g.K : g.N;
+        if (g.stride_a < g.lda * a_cols || g.stride_b < g.ldb * b_cols || g.stride_d < g.ldd * g.N ||
+            (g.beta != 0.0f && g.stride_c < g.ldc * g.N))
+            return no("batch strides must be at least the extent of one matrix");
+        if ((g.stride_a % 8) || (g.stride_b % 8) || (g.stride_d % d_quant) || (g.beta != 0.0f && (g.stride_c % c_quant)))
+            return no("batch strides must be multiples of 16 bytes for TMA");
+    }
     return true;
 }
 
@@ -141,21 +168,36 @@ int gemm_tcgen05_launch(const GemmProblem& g, const GemmPlan& plan, float* scrat
     if (b_mn && (bn_local % 64)) return fail(B200_UNSUPPORTED, "row-major B needs at least 64 tile columns per CTA");
     if (q.split_k > 1 && !scratch) return fail(B200_INVALID_ARG, "split-K launch without scratch");
 
+    const bool batched = g.batch > 1;
+    auto batch_dim = [&](int64_t stride) {
+        BatchDim b;
+        if (batched) {
+            b.count = g.batch;
+            b.stride = stride;
+        }
+        return b;
+    };
+    auto map_type = [](int type) {
+        return type == B200_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                : (type == B200_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
+    };
+    const CUtensorMapDataType ab_dt = map_type(g.ab_type);
+
     CUtensorMap tmA, tmB, tmC, tmD;
     int rc;
     if (a_mn)
-        rc = make_map_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.A, g.M, g.K, g.lda, 64, 64,
-                         CU_TENSOR_MAP_SWIZZLE_128B, "A (column-major)");
+        rc = make_map_2d(&tmA, ab_dt, 2, g.A, g.M, g.K, g.lda, 64, 64, CU_TENSOR_MAP_SWIZZLE_128B, "A (column-major)",
+                         batch_dim(g.stride_a));
     else
-        rc = make_map_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.A, g.K, g.M, g.lda, 64, 128,
-                         CU_TENSOR_MAP_SWIZZLE_128B, "A (row-major)");
+        rc = make_map_2d(&tmA, ab_dt, 2, g.A, g.K, g.M, g.lda, 64, 128, CU_TENSOR_MAP_SWIZZLE_128B, "A (row-major)",
+                         batch_dim(g.stride_a));
     if (rc) return rc;
     if (b_mn)
-        rc = make_map_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.B, g.N, g.K, g.ldb, 64, 64,
-                         CU_TENSOR_MAP_SWIZZLE_128B, "B (row-major)");
+        rc = make_map_2d(&tmB, ab_dt, 2, g.B, g.N, g.K, g.ldb, 64, 64, CU_TENSOR_MAP_SWIZZLE_128B, "B (row-major)",
+                         batch_dim(g.stride_b));
     else
-        rc = make_map_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.B, g.K, g.N, g.ldb, 64, bn_local,
-                         CU_TENSOR_MAP_SWIZZLE_128B, "B (column-major)");
+        rc = make_map_2d(&tmB, ab_dt, 2, g.B, g.K, g.N, g.ldb, 64, bn_local, CU_TENSOR_MAP_SWIZZLE_128B,
+                         "B (column-major)", batch_dim(g.stride_b));
     if (rc) return rc;
 
     GemmParams p = {};
@@ -176,6 +218,8 @@ int gemm_tcgen05_launch(const GemmProblem& g, const GemmPlan& plan, float* scrat
     }
     p.status = status_word;
     p.wait_budget_ns = plan.wait_budget_ns;
+    p.ab_bf16 = g.ab_type == B200_BF16 ? 1 : 0;
+    p.batch = static_cast<int>(g.batch);
 
     if (q.split_k > 1) {
         // partial products go to scratch (k-slice s occupies columns [s * stride, s * stride + N))
@@ -187,13 +231,12 @@ int gemm_tcgen05_launch(const GemmProblem& g, const GemmPlan& plan, float* scrat
         p.beta = 0.0f;
         p.out_n_stride = q.ws_n_stride;
     } else {
-        const bool dh = g.d_type == B200_F16, ch = g.c_type == B200_F16;
-        rc = make_map_2d(&tmD, dh ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, dh ? 2 : 4, g.D, g.M,
-                         g.N, g.ldd, 128, 32, CU_TENSOR_MAP_SWIZZLE_NONE, "D");
+        rc = make_map_2d(&tmD, map_type(g.d_type), elem_bytes(g.d_type), g.D, g.M, g.N, g.ldd, 128, 32,
+                         CU_TENSOR_MAP_SWIZZLE_NONE, "D", batch_dim(g.stride_d));
         if (rc) return rc;
         if (g.beta != 0.0f) {
-            rc = make_map_2d(&tmC, ch ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, ch ? 2 : 4, g.C,
-                             g.M, g.N, g.ldc, 128, 32, CU_TENSOR_MAP_SWIZZLE_NONE, "C");
+            rc = make_map_2d(&tmC, map_type(g.c_type), elem_bytes(g.c_type), g.C, g.M, g.N, g.ldc, 128, 32,
+                             CU_TENSOR_MAP_SWIZZLE_NONE, "C", batch_dim(g.stride_c));
             if (rc) return rc;
         } else {
             tmC = tmD;  // never dereferenced
@@ -201,11 +244,11 @@ int gemm_tcgen05_launch(const GemmProblem& g, const GemmPlan& plan, float* scrat
         p.alpha = g.alpha;
         p.beta = g.beta;
         p.out_n_stride = 0;
-        p.c_f16 = ch ? 1 : 0;
-        p.d_f16 = dh ? 1 : 0;
+        p.c_fmt = elem_fmt(g.c_type);
+        p.d_fmt = elem_fmt(g.d_type);
     }
 
-    const int units = q.tiles_m * q.tiles_n * q.split_k;
+    const int units = q.tiles_m * q.tiles_n * (batched ? static_cast<int>(g.batch) : q.split_k);
     int cap = plan.max_ctas > 0 ? plan.max_ctas : sm_count;
     if (cap > sm_count) cap = sm_count;
     int grid;
@@ -240,8 +283,8 @@ int gemm_tcgen05_launch(const GemmProblem& g, const GemmPlan& plan, float* scrat
         if (blocks > sm_count * 8) blocks = sm_count * 8;
         if (blocks < 1) blocks = 1;
         gemm_splitk_reduce<<<blocks, 256, 0, stream>>>(scratch, q.ws_ld, q.ws_n_stride, q.split_k, p.M, p.N, g.alpha,
-                                                       g.beta, g.C, g.ldc, g.D, g.ldd, vec_ok ? 1 : 0, g.c_type == B200_F16 ? 1 : 0,
-                                                       g.d_type == B200_F16 ? 1 : 0);
+                                                       g.beta, g.C, g.ldc, g.D, g.ldd, vec_ok ? 1 : 0, elem_fmt(g.c_type),
+                                                       elem_fmt(g.d_type));
         B200_CUDA_TRY(cudaGetLastError());
     }
     if (info) {

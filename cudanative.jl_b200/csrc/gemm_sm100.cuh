@@ -23,6 +23,9 @@
 // Work units are (tile, k-slice) pairs; with split_k > 1 each unit writes a raw FP32 partial
 // product to a scratch matrix and a second kernel reduces them (gemm_splitk_reduce).
 //
+// Batched problems (kBatch) run the same pipeline over 3-D tensor maps whose outermost coordinate is
+// the matrix of the batch; a work unit is then (matrix, tile) and split-K is not used.
+//
 // Every barrier wait is bounded (ptx_sm100.cuh: mbar_wait); on expiry the CTA records the wait
 // in the device status word and every role falls through to the common exit.
 #pragma once
@@ -45,7 +48,9 @@ struct GemmParams {
     // panel has arrived in this GPU's memory).  At most 32 panels.
     const unsigned int* panel_flags;
     int kb_per_panel;
-    int c_f16, d_f16;      // element types of C and D in memory: 0 = binary32, 1 = binary16
+    int c_fmt, d_fmt;      // element types of C and D in memory: 0 = binary32, 1 = binary16, 2 = bfloat16
+    int ab_bf16;           // A and B are bfloat16 instead of binary16
+    int batch;             // matrices per launch (kBatch kernels; the tensor maps are 3-D then)
     int* status;
     unsigned long long wait_budget_ns;
 };
@@ -89,7 +94,7 @@ __device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& 
     tn = idx / rows;
 }
 
-template <int kBN, bool kAMn, bool kBMn, int kCtas>
+template <int kBN, bool kAMn, bool kBMn, int kCtas, bool kBatch = false>
 __global__ void __launch_bounds__(256, 1)
 gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmD,
@@ -122,7 +127,8 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const uint32_t cta_rank = kPair ? cluster_cta_rank() : 0u;
     const int unit_stride = kPair ? (gridDim.x >> 1) : gridDim.x;
     const int unit_first = kPair ? (blockIdx.x >> 1) : blockIdx.x;
-    const int num_units = p.tiles_m * p.tiles_n * p.split_k;
+    const int tiles_per_matrix = p.tiles_m * p.tiles_n;
+    const int num_units = kBatch ? tiles_per_matrix * p.batch : tiles_per_matrix * p.split_k;
 
     WaitCtx wc{abort_flag, p.status, p.wait_budget_ns};
 
@@ -150,10 +156,18 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
-    // unit -> (tile row, tile col, k-block range)
-    auto unit_decode = [&](int unit, int& m0, int& n0, int& kb0, int& kb1, int& out_n0) {
-        const int tile = unit / p.split_k;
-        const int slice = unit - tile * p.split_k;
+    // unit -> (tile row, tile col, k-block range, matrix of the batch)
+    auto unit_decode = [&](int unit, int& m0, int& n0, int& kb0, int& kb1, int& out_n0, int& bz) {
+        int tile, slice;
+        if constexpr (kBatch) {
+            bz = unit / tiles_per_matrix;
+            tile = unit - bz * tiles_per_matrix;
+            slice = 0;
+        } else {
+            bz = 0;
+            tile = unit / p.split_k;
+            slice = unit - tile * p.split_k;
+        }
         int tm, tn;
         tile_coords(p, tile, tm, tn);
         m0 = tm * (Cfg::BM * kCtas) + static_cast<int>(cta_rank) * Cfg::BM;
@@ -161,6 +175,19 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         kb0 = slice * p.kb_per_split;
         kb1 = min(p.kb_total, kb0 + p.kb_per_split);
         out_n0 = n0 + slice * p.out_n_stride;
+    };
+    // TMA copies of C / D chunks (2-D maps, or 3-D with the matrix index when batched)
+    auto load_c_chunk = [&](uint32_t dst, int x, int y, int z, uint32_t bar, uint64_t policy) {
+        if constexpr (kBatch) tma_load_3d_hint(dst, &tmC, x, y, z, bar, policy);
+        else tma_load_2d_hint(dst, &tmC, x, y, bar, policy);
+    };
+    auto store_d_chunk = [&](int x, int y, int z, uint32_t src, uint64_t policy, bool hinted) {
+        if constexpr (kBatch) {
+            tma_store_3d_hint(&tmD, x, y, z, src, policy);
+        } else {
+            if (hinted) tma_store_2d_hint(&tmD, x, y, src, policy);
+            else tma_store_2d(&tmD, x, y, src);  // partial products are read back by the reduction right away
+        }
     };
 
     if (warp == 0) {
@@ -175,8 +202,12 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             // CTA re-reads from L2.
             const bool a_once = (p.tiles_n == 1);
             const uint64_t once_policy = l2_policy_evict_first();
+            int bz = 0;  // matrix of the batch the current unit belongs to
             auto load_a = [&](uint32_t dst, int x, int y, uint32_t bar) {
-                if constexpr (kPair) {
+                if constexpr (kBatch) {
+                    if constexpr (kPair) tma_load_3d_pair(dst, &tmA, x, y, bz, bar);
+                    else tma_load_3d(dst, &tmA, x, y, bz, bar);
+                } else if constexpr (kPair) {
                     if (a_once) tma_load_2d_pair_hint(dst, &tmA, x, y, bar, once_policy);
                     else tma_load_2d_pair(dst, &tmA, x, y, bar);
                 } else {
@@ -184,12 +215,22 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     else tma_load_2d(dst, &tmA, x, y, bar);
                 }
             };
+            auto load_b = [&](uint32_t dst, int x, int y, uint32_t bar) {
+                if constexpr (kBatch) {
+                    if constexpr (kPair) tma_load_3d_pair(dst, &tmB, x, y, bz, bar);
+                    else tma_load_3d(dst, &tmB, x, y, bz, bar);
+                } else if constexpr (kPair) {
+                    tma_load_2d_pair(dst, &tmB, x, y, bar);
+                } else {
+                    tma_load_2d(dst, &tmB, x, y, bar);
+                }
+            };
 #ifdef B200_PROBE_SKIP_LOADS
             uint32_t issued = 0;
 #endif
             for (int unit = unit_first; ok && unit < num_units; unit += unit_stride) {
                 int m0, n0, kb0, kb1, out_n0;
-                unit_decode(unit, m0, n0, kb0, kb1, out_n0);
+                unit_decode(unit, m0, n0, kb0, kb1, out_n0, bz);
                 const int nb0 = n0 + static_cast<int>(cta_rank) * Cfg::BN_LOCAL;
                 for (int kb = kb0; kb < kb1; ++kb, s = (s + 1 == STAGES ? 0 : s + 1), ph ^= (s == 0)) {
                     if (panels_seen != 0xffffffffu) {
@@ -225,9 +266,9 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                         if constexpr (kBMn) {
 #pragma unroll
                             for (int i = 0; i < Cfg::BN_LOCAL / 64; ++i)
-                                tma_load_2d(sb + i * 8192, &tmB, nb0 + i * 64, k0, fb);
+                                load_b(sb + i * 8192, nb0 + i * 64, k0, fb);
                         } else {
-                            tma_load_2d(sb, &tmB, k0, nb0, fb);
+                            load_b(sb, k0, nb0, fb);
                         }
                     } else {
                         // Both CTAs' loads complete on the leader's barrier.  Only the leader
@@ -246,9 +287,9 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                         if constexpr (kBMn) {
 #pragma unroll
                             for (int i = 0; i < Cfg::BN_LOCAL / 64; ++i)
-                                tma_load_2d_pair(sb + i * 8192, &tmB, nb0 + i * 64, k0, fb);
+                                load_b(sb + i * 8192, nb0 + i * 64, k0, fb);
                         } else {
-                            tma_load_2d_pair(sb, &tmB, k0, nb0, fb);
+                            load_b(sb, k0, nb0, fb);
                         }
                     }
                 }
@@ -258,8 +299,9 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0 && cta_rank == 0) {
-            constexpr uint32_t idesc =
-                make_idesc_f16_f32(Cfg::BM * kCtas, kBN, kAMn ? 1 : 0, kBMn ? 1 : 0);
+            const uint32_t idesc = p.ab_bf16
+                ? make_idesc_f16_f32(Cfg::BM * kCtas, kBN, kAMn ? 1 : 0, kBMn ? 1 : 0, 1)
+                : make_idesc_f16_f32(Cfg::BM * kCtas, kBN, kAMn ? 1 : 0, kBMn ? 1 : 0, 0);
             // Descriptors differ between stages and k-steps only in their start-address field
             // (bits [0,14), in units of 16 bytes): build them once and add offsets.
             // K-major tile: rows of 128 B, 8-row groups 1 KiB apart, k = 16 advances 32 B inside
@@ -274,8 +316,8 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             uint32_t ph = 0, ucount = 0;
             bool ok = true;
             for (int unit = unit_first; ok && unit < num_units; unit += unit_stride, ++ucount) {
-                int m0, n0, kb0, kb1, out_n0;
-                unit_decode(unit, m0, n0, kb0, kb1, out_n0);
+                int m0, n0, kb0, kb1, out_n0, bz;
+                unit_decode(unit, m0, n0, kb0, kb1, out_n0, bz);
                 const uint32_t acc = ucount & 1u;
                 const uint32_t aph = (ucount >> 1) & 1u;
                 ok = mbar_wait(tmem_empty_bar(acc), aph ^ 1u, wc, kWaitTmemEmpty);
@@ -320,11 +362,12 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         const bool elected = (et == 0);
         const bool has_c = (p.beta != 0.0f);
         const float alpha = p.alpha, beta = p.beta;
-        const bool c_f16 = p.c_f16 != 0, d_f16 = p.d_f16 != 0;
-        const uint32_t c_chunk_bytes = c_f16 ? Cfg::EPI_BYTES / 2 : Cfg::EPI_BYTES;
+        const bool c_half = p.c_fmt != 0, d_half = p.d_fmt != 0;  // 2-byte elements
+        const bool c_bf16 = p.c_fmt == 2, d_bf16 = p.d_fmt == 2;
+        const uint32_t c_chunk_bytes = c_half ? Cfg::EPI_BYTES / 2 : Cfg::EPI_BYTES;
         // C is updated in place in the staging buffer only if D has the same element size; otherwise
         // every thread must have read its C values before anybody writes D over them
-        const bool two_phase = has_c && (c_f16 != d_f16);
+        const bool two_phase = has_c && (c_half != d_half);
 
         auto chunks_of = [&](int n0) { return min(Cfg::NCHUNK, (p.N - n0 + Cfg::EPI_COLS - 1) / Cfg::EPI_COLS); };
 
@@ -332,16 +375,16 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         const uint64_t stream_policy = l2_policy_evict_first();
         uint32_t g = 0;  // chunk counter: staging buffer g & 1, C-barrier phase (g >> 1) & 1
         if (has_c && elected && unit_first < num_units) {
-            int m0, n0, kb0, kb1, out_n0;
-            unit_decode(unit_first, m0, n0, kb0, kb1, out_n0);
+            int m0, n0, kb0, kb1, out_n0, bz;
+            unit_decode(unit_first, m0, n0, kb0, kb1, out_n0, bz);
             mbar_arrive_expect_tx(cfull_bar(0), c_chunk_bytes);
-            tma_load_2d_hint(epi_base, &tmC, m0, n0, cfull_bar(0), stream_policy);
+            load_c_chunk(epi_base, m0, n0, bz, cfull_bar(0), stream_policy);
         }
         uint32_t ucount = 0;
         bool fail = false;
         for (int unit = unit_first; unit < num_units; unit += unit_stride, ++ucount) {
-            int m0, n0, kb0, kb1, out_n0;
-            unit_decode(unit, m0, n0, kb0, kb1, out_n0);
+            int m0, n0, kb0, kb1, out_n0, bz;
+            unit_decode(unit, m0, n0, kb0, kb1, out_n0, bz);
             const int nchunks = chunks_of(n0);
             const uint32_t acc = ucount & 1u;
             const uint32_t aph = (ucount >> 1) & 1u;
@@ -353,18 +396,18 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     if (has_c) {
                         // fetch the next chunk of C into the other buffer once the store that
                         // last used it has finished reading shared memory
-                        int nm0 = m0, nn0 = n0 + (j + 1) * Cfg::EPI_COLS;
+                        int nm0 = m0, nn0 = n0 + (j + 1) * Cfg::EPI_COLS, nbz = bz;
                         bool have_next = (j + 1 < nchunks);
                         if (!have_next && unit + unit_stride < num_units) {
                             int a, b, c;
-                            unit_decode(unit + unit_stride, nm0, nn0, a, b, c);
+                            unit_decode(unit + unit_stride, nm0, nn0, a, b, c, nbz);
                             have_next = true;
                         }
                         if (have_next) {
                             tma_store_wait_read<0>();
                             mbar_arrive_expect_tx(cfull_bar(buf ^ 1u), c_chunk_bytes);
-                            tma_load_2d_hint(epi_base + (buf ^ 1u) * Cfg::EPI_BYTES, &tmC, nm0, nn0,
-                                             cfull_bar(buf ^ 1u), stream_policy);
+                            load_c_chunk(epi_base + (buf ^ 1u) * Cfg::EPI_BYTES, nm0, nn0, nbz, cfull_bar(buf ^ 1u),
+                                         stream_policy);
                         }
                     } else {
                         tma_store_wait_read<1>();
@@ -379,11 +422,16 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 uint32_t r[32];
                 float* col = epi_gen + buf * (Cfg::EPI_BYTES / 4) + et;                      // binary32 view
                 __half* colh = reinterpret_cast<__half*>(epi_gen + buf * (Cfg::EPI_BYTES / 4)) + et;  // binary16 view
+                __nv_bfloat16* colb = reinterpret_cast<__nv_bfloat16*>(colh);                        // bfloat16 view
                 if (ok) {
                     tmem_ld_32x32b_x32(tmem_base + lane_base + acc * kBN + j * Cfg::EPI_COLS, r);
                     tmem_wait_ld();
                     if (has_c) {
-                        if (c_f16) {
+                        if (c_bf16) {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                r[i] = __float_as_uint(fmaf(alpha, __uint_as_float(r[i]), beta * __bfloat162float(colb[i * Cfg::BM])));
+                        } else if (c_half) {
 #pragma unroll
                             for (int i = 0; i < 32; ++i)
                                 r[i] = __float_as_uint(fmaf(alpha, __uint_as_float(r[i]), beta * __half2float(colh[i * Cfg::BM])));
@@ -399,7 +447,10 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 }
                 if (two_phase) named_bar_sync(3, 128);
                 if (ok) {
-                    if (d_f16) {
+                    if (d_bf16) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) colb[i * Cfg::BM] = __float2bfloat16_rn(__uint_as_float(r[i]));
+                    } else if (d_half) {
 #pragma unroll
                         for (int i = 0; i < 32; ++i) colh[i * Cfg::BM] = __float2half_rn(__uint_as_float(r[i]));
                     } else {
@@ -411,11 +462,8 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 fail = named_bar_or(2, 128, !ok);
                 if (fail) break;
                 if (elected && m0 < p.M) {  // a pair's second CTA may own no rows of a bottom-edge tile
-                    if (p.split_k > 1)  // partial products are read back by the reduction right away
-                        tma_store_2d(&tmD, m0, out_n0 + j * Cfg::EPI_COLS, epi_base + buf * Cfg::EPI_BYTES);
-                    else
-                        tma_store_2d_hint(&tmD, m0, out_n0 + j * Cfg::EPI_COLS, epi_base + buf * Cfg::EPI_BYTES,
-                                          stream_policy);
+                    store_d_chunk(m0, out_n0 + j * Cfg::EPI_COLS, bz, epi_base + buf * Cfg::EPI_BYTES, stream_policy,
+                                  p.split_k <= 1);
                     tma_store_commit();
                 }
             }
@@ -451,11 +499,13 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 __global__ void gemm_splitk_reduce(const float* __restrict__ ws, long long ldw, int n_stride,
                                    int split_k, int M, int N, float alpha, float beta,
                                    const void* __restrict__ Cv, long long ldc, void* __restrict__ Dv,
-                                   long long ldd, int vec_ok, int c_f16, int d_f16) {
+                                   long long ldd, int vec_ok, int c_fmt, int d_fmt) {
     const float* C = static_cast<const float*>(Cv);
     float* D = static_cast<float*>(Dv);
     const __half* Ch = static_cast<const __half*>(Cv);
     __half* Dh = static_cast<__half*>(Dv);
+    const __nv_bfloat16* Cb = static_cast<const __nv_bfloat16*>(Cv);
+    __nv_bfloat16* Db = static_cast<__nv_bfloat16*>(Dv);
     const long long quads_m = (M + 3) / 4;
     const long long total = quads_m * N;
     for (long long q = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; q < total;
@@ -480,9 +530,14 @@ __global__ void gemm_splitk_reduce(const float* __restrict__ ws, long long ldw, 
                 float acc = 0.f;
                 for (int s = 0; s < split_k; ++s) acc += ws[(n + static_cast<long long>(s) * n_stride) * ldw + m + i];
                 float out = alpha * acc;
-                if (beta != 0.0f) out = fmaf(beta, c_f16 ? __half2float(Ch[n * ldc + m + i]) : C[n * ldc + m + i], out);
-                if (d_f16) Dh[n * ldd + m + i] = __float2half_rn(out);
-                else D[n * ldd + m + i] = out;
+                if (beta != 0.0f) {
+                    const long long ci = n * ldc + m + i;
+                    out = fmaf(beta, c_fmt == 2 ? __bfloat162float(Cb[ci]) : c_fmt == 1 ? __half2float(Ch[ci]) : C[ci], out);
+                }
+                const long long di = n * ldd + m + i;
+                if (d_fmt == 2) Db[di] = __float2bfloat16_rn(out);
+                else if (d_fmt == 1) Dh[di] = __float2half_rn(out);
+                else D[di] = out;
             }
         }
     }

@@ -41,9 +41,17 @@ struct GemmProblem {
     // above point at binary16 data and ldc / ldd count binary16 elements
     int c_type = B200_F32;
     int d_type = B200_F32;
+    // element type of A and B: B200_F16 or B200_BF16 (both operands the same)
+    int ab_type = B200_F16;
+    // batched problems: `batch` independent products; matrix i of X starts stride_x * i elements after
+    // X (a stride of 0 repeats the matrix).  batch == 1 ignores the strides.
+    int64_t batch = 1;
+    int64_t stride_a = 0, stride_b = 0, stride_c = 0, stride_d = 0;
 };
 
-inline int elem_bytes(int type) { return type == B200_F16 ? 2 : 4; }
+inline int elem_bytes(int type) { return type == B200_F32 ? 4 : 2; }
+// 0 = binary32, 1 = binary16, 2 = bfloat16: the encoding the kernels take
+inline int elem_fmt(int type) { return type == B200_F32 ? 0 : (type == B200_F16 ? 1 : 2); }
 
 struct GemmPlan {
     int tile_n;    // 64 / 128 / 256

@@ -7,6 +7,7 @@
 #pragma once
 
 #include <cuda.h>
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -270,6 +271,60 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* tm, int x, int y
                  : "memory");
 }
 
+// 3-D forms of the copies above for batched problems: z selects the matrix of the batch (box extent 1
+// in that dimension, so the shared-memory image of a tile is the same as in the 2-D case).
+__device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const CUtensorMap* tm, int x, int y, int z,
+                                            uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst_smem),
+        "l"(reinterpret_cast<uint64_t>(tm)), "r"(x), "r"(y), "r"(z), "r"(bar)
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst_smem, const CUtensorMap* tm, int x, int y, int z,
+                                                 uint32_t bar_cluster_addr) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst_smem),
+        "l"(reinterpret_cast<uint64_t>(tm)), "r"(x), "r"(y), "r"(z), "r"(bar_cluster_addr)
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_load_3d_hint(uint32_t dst_smem, const CUtensorMap* tm, int x, int y, int z,
+                                                 uint32_t bar, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+        "[%0], [%1, {%2, %3, %4}], [%5], %6;" ::"r"(dst_smem),
+        "l"(reinterpret_cast<uint64_t>(tm)), "r"(x), "r"(y), "r"(z), "r"(bar), "l"(policy)
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_load_3d_pair_hint(uint32_t dst_smem, const CUtensorMap* tm, int x, int y,
+                                                      int z, uint32_t bar_cluster_addr, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+        "[%0], [%1, {%2, %3, %4}], [%5], %6;" ::"r"(dst_smem),
+        "l"(reinterpret_cast<uint64_t>(tm)), "r"(x), "r"(y), "r"(z), "r"(bar_cluster_addr), "l"(policy)
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* tm, int x, int y, int z, uint32_t src_smem) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];" ::"l"(
+                     reinterpret_cast<uint64_t>(tm)),
+                 "r"(x), "r"(y), "r"(z), "r"(src_smem)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tma_store_3d_hint(const CUtensorMap* tm, int x, int y, int z, uint32_t src_smem,
+                                                  uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%1, %2, %3}], [%4], %5;" ::"l"(
+            reinterpret_cast<uint64_t>(tm)),
+        "r"(x), "r"(y), "r"(z), "r"(src_smem), "l"(policy)
+        : "memory");
+}
+
 __device__ __forceinline__ void tma_store_commit() {
     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
@@ -330,13 +385,13 @@ __device__ __forceinline__ void tc_fence_after_sync() {
 // ---------------------------------------------------------------------------------------------
 // tcgen05: descriptors
 // ---------------------------------------------------------------------------------------------
-// Instruction descriptor of tcgen05.mma.kind::f16 with binary16 A and B and a binary32
-// accumulator.  Bit layout (PTX ISA, "Instruction descriptor"): [4,6) D format (1 = F32),
-// [7,10) A format (0 = F16), [10,13) B format, [15] A major (0 = K, 1 = MN), [16] B major,
+// Instruction descriptor of tcgen05.mma.kind::f16 with binary16 (or, ab_bf16 = 1, bfloat16) A and
+// B and a binary32 accumulator.  Bit layout (PTX ISA, "Instruction descriptor"): [4,6) D format
+// (1 = F32), [7,10) A format (0 = F16, 1 = BF16), [10,13) B format, [15] A major (0 = K, 1 = MN), [16] B major,
 // [17,23) N >> 3, [24,29) M >> 4.
 __host__ __device__ constexpr uint32_t make_idesc_f16_f32(int m, int n, int a_mn_major,
-                                                          int b_mn_major) {
-    return (1u << 4) | (0u << 7) | (0u << 10) | (static_cast<uint32_t>(a_mn_major) << 15) |
+                                                          int b_mn_major, int ab_bf16 = 0) {
+    return (1u << 4) | (static_cast<uint32_t>(ab_bf16) << 7) | (static_cast<uint32_t>(ab_bf16) << 10) | (static_cast<uint32_t>(a_mn_major) << 15) |
            (static_cast<uint32_t>(b_mn_major) << 16) | (static_cast<uint32_t>(n >> 3) << 17) |
            (static_cast<uint32_t>(m >> 4) << 24);
 }

@@ -18,6 +18,19 @@ import numpy as np
 
 from . import _lib
 from .array import CuHostArray, DevicePtr
+from .bfloat16 import BFloat16
+
+
+def _type_code(t) -> int:
+    """numpy dtype (float16 / float32) or the ``BFloat16`` tag -> the library's element tag."""
+    if t is BFloat16:
+        return _lib.BF16
+    dt = np.dtype(t)
+    if dt == np.float16:
+        return _lib.F16
+    if dt == np.float32:
+        return _lib.F32
+    raise TypeError(f"invalid element type {t!r}: Float16, BFloat16 or Float32")
 
 
 class Handle:
@@ -85,6 +98,25 @@ class Handle:
         _lib.check(_lib.lib().b200_gemm_f16_typed(self._h, stream, int(bool(transA)), int(bool(transB)), M, N, K,
                                                   float(alpha), a, lda, b, ldb, float(beta), c, ldc, code[np.dtype(c_type)],
                                                   d, ldd, code[np.dtype(d_type)]), "gemm_typed")
+
+    def gemm_ex(self, transA: bool, transB: bool, M: int, N: int, K: int, alpha: float, A, lda: int, B, ldb: int,
+                ab_type, beta: float, Cm, ldc: int, c_type, D, ldd: int, d_type, stream=None) -> None:
+        """``gemm`` with A and B both Float16 or both ``BFloat16`` and C, D each Float16, ``BFloat16`` or
+        Float32 (b200_gemm_ex); accumulation is binary32 throughout."""
+        self.gemm_strided_batched(transA, transB, M, N, K, alpha, A, lda, 0, B, ldb, 0, ab_type, beta, Cm, ldc, 0,
+                                  c_type, D, ldd, 0, d_type, 1, stream=stream)
+
+    def gemm_strided_batched(self, transA: bool, transB: bool, M: int, N: int, K: int, alpha: float, A, lda: int,
+                             stride_a: int, B, ldb: int, stride_b: int, ab_type, beta: float, Cm, ldc: int,
+                             stride_c: int, c_type, D, ldd: int, stride_d: int, d_type, batch: int, stream=None) -> None:
+        """``batch`` products of one shape, matrix i of X starting ``stride_x * i`` elements after X
+        (b200_gemm_strided_batched); a stride of 0 repeats A, B or C."""
+        a, b, d = _addr(A), _addr(B), _addr(D)
+        c = _addr(Cm) if Cm is not None else None
+        _lib.check(_lib.lib().b200_gemm_strided_batched(
+            self._h, stream, int(bool(transA)), int(bool(transB)), M, N, K, float(alpha), a, lda, stride_a, b, ldb,
+            stride_b, _type_code(ab_type), float(beta), c, ldc, stride_c, _type_code(c_type), d, ldd, stride_d,
+            _type_code(d_type), batch), "gemm_strided_batched")
 
     def gemm_gated(self, transA: bool, transB: bool, M: int, N: int, K: int, alpha: float, A, lda: int, B, ldb: int,
                    beta: float, Cm, ldc: int, D, ldd: int, panel_flags, panel_k: int, stream=None) -> None:

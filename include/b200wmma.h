@@ -36,8 +36,10 @@ enum {
 /* Layout tags: the reference's WMMA.ColMajor / WMMA.RowMajor (src/device/cuda/wmma.jl:313-338). */
 enum { B200_COL_MAJOR = 0, B200_ROW_MAJOR = 1 };
 
-/* Element tags: Float16 / Float32, the two WMMA element types (src/device/cuda/wmma.jl:11-37). */
-enum { B200_F16 = 0, B200_F32 = 1 };
+/* Element tags: Float16 / Float32, the two WMMA element types (src/device/cuda/wmma.jl:11-37).
+ * B200_BF16 (bfloat16) has no counterpart in the reference; only b200_gemm_ex and
+ * b200_gemm_strided_batched accept it. */
+enum { B200_F16 = 0, B200_F32 = 1, B200_BF16 = 2 };
 
 /* Fragment use: WMMA.MatrixA / MatrixB / Accumulator (src/device/cuda/wmma.jl:343-346). */
 enum { B200_MATRIX_A = 0, B200_MATRIX_B = 1, B200_ACCUMULATOR = 2 };
@@ -145,6 +147,32 @@ int b200_gemm_f16_typed(b200_handle* h, b200_stream stream, int transA, int tran
                         int64_t N, int64_t K, float alpha, const void* A, int64_t lda,
                         const void* B, int64_t ldb, float beta, const void* C, int64_t ldc,
                         int c_type, void* D, int64_t ldd, int d_type);
+
+/* The general form of the two entry points above: A and B are both binary16 (ab_type = B200_F16) or
+ * both bfloat16 (B200_BF16); C and D are binary32, binary16 or bfloat16 independently.  Products
+ * of two bfloat16 values are exact in binary32 as well, accumulation stays binary32, a 16-bit D
+ * is rounded once to nearest even.  Leading dimensions count elements of the respective type.
+ * No counterpart in the reference beyond the Float16 / Float32 combinations of
+ * b200_gemm_f16_typed: bfloat16 is what callers of a tensor-core product expect next to them. */
+int b200_gemm_ex(b200_handle* h, b200_stream stream, int transA, int transB, int64_t M, int64_t N,
+                 int64_t K, float alpha, const void* A, int64_t lda, const void* B, int64_t ldb,
+                 int ab_type, float beta, const void* C, int64_t ldc, int c_type, void* D,
+                 int64_t ldd, int d_type);
+
+/* `batch` independent products of one shape in one call:
+ *     D_i = alpha * op(A_i) * op(B_i) + beta * C_i,   X_i = X + i * stride_x elements,  i < batch
+ * (no counterpart in the reference, which stops at one 16x16x16 tile per warp).  A stride of 0
+ * repeats A, B or C for every i; D_i must not overlap (stride_d >= ldd * N).  batch == 0 is a
+ * no-op.  One launch runs every tile of every matrix when the strides are multiples of 16 bytes
+ * and at least one matrix long (the matrix index is a third TMA coordinate); otherwise the
+ * matrices are multiplied one launch each, or all on the simple kernel.  Types as in
+ * b200_gemm_ex.  The split-K option is ignored for batches. */
+int b200_gemm_strided_batched(b200_handle* h, b200_stream stream, int transA, int transB,
+                              int64_t M, int64_t N, int64_t K, float alpha, const void* A,
+                              int64_t lda, int64_t stride_a, const void* B, int64_t ldb,
+                              int64_t stride_b, int ab_type, float beta, const void* C,
+                              int64_t ldc, int64_t stride_c, int c_type, void* D, int64_t ldd,
+                              int64_t stride_d, int d_type, int64_t batch);
 
 /* b200_gemm_f16f32 whose main loop may start before all of A is in this GPU's memory: columns
  * [j*panel_k, (j+1)*panel_k) of op(A) are read only once the 32-bit word panel_flags[j] (device
@@ -303,9 +331,11 @@ int b200_p2p_exchange(int rank, int world, int64_t M, const int64_t* sub_cols, i
  * dist 0: uniform[-1,1) = (u >> 40) * 2^-23 - 1
  * dist 1: normal(0,1) by Box-Muller on the two 24-bit halves of u's top 48 bits
  * dist 2: zeros
- * times `scale`, then (f16 variant) rounded to nearest-even binary16. */
+ * times `scale`, then (f16 / bf16 variants) rounded to nearest-even binary16 / bfloat16. */
 int b200_fill_f16(b200_stream stream, void* dptr, int64_t rows, int64_t cols, int64_t ld,
                   uint64_t seed, uint64_t matrix_id, uint64_t index0, int dist, float scale);
+int b200_fill_bf16(b200_stream stream, void* dptr, int64_t rows, int64_t cols, int64_t ld,
+                   uint64_t seed, uint64_t matrix_id, uint64_t index0, int dist, float scale);
 int b200_fill_f32(b200_stream stream, float* dptr, int64_t rows, int64_t cols, int64_t ld,
                   uint64_t seed, uint64_t matrix_id, uint64_t index0, int dist, float scale);
 
