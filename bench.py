@@ -9,6 +9,10 @@ Workloads (all synthetic, from the counter-based generator of the library):
     skinny    M=16384, N=128, K=8192, A, B column-major, beta=0, seed 3              (HBM-bound)
     sharded   M=N=32768, K=16384, A, B column-major, alpha=beta=1, seed 4; B/C/D split into
               column slabs over the ranks, A broadcast from rank 0 with NCCL        (default at N>1)
+Secondary workloads (1 GPU, device-resident timing only; no e2e / CPU leg):
+    gemm8192_bf16  gemm8192 with bfloat16 A and B (b200_gemm_ex)
+    batched64      64 products of 1024^3, Float16 in, Float32 C and D, alpha=beta=1, one launch
+                   (b200_gemm_strided_batched); also timed as 64 launches of b200_gemm_f16f32
 
 A "step" is one whole GEMM.  `value` is the whole job's TFLOP/s with operands resident in HBM,
 timed with CUDA events on the launching stream (max over ranks); `e2e` is the same metric through
@@ -40,6 +44,11 @@ WORKLOADS = {
     "gemm4096": dict(M=4096, N=4096, K=4096, transA=False, transB=False, alpha=1.0, beta=1.0, seed=1, b_rsqrt=True, c_dist="normal"),
     "skinny": dict(M=16384, N=128, K=8192, transA=False, transB=False, alpha=1.0, beta=0.0, seed=3, b_rsqrt=False, c_dist="zeros"),
     "sharded": dict(M=32768, N=32768, K=16384, transA=False, transB=False, alpha=1.0, beta=1.0, seed=4, b_rsqrt=True, c_dist="normal"),
+}
+# device-resident timing of the bfloat16 and batched entry points (run_extra)
+EXTRA_WORKLOADS = {
+    "gemm8192_bf16": dict(M=8192, N=8192, K=8192, batch=1, transA=True, transB=False, alpha=2.0, beta=0.5, seed=2, bf16=True),
+    "batched64": dict(M=1024, N=1024, K=1024, batch=64, transA=False, transB=False, alpha=1.0, beta=1.0, seed=5, bf16=False),
 }
 METRIC = "FP16->FP32 GEMM TFLOP/s (8192^3) & % of B200 tensor peak; 1/2/4/8-GPU scaling"
 
@@ -391,6 +400,95 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_extra(args):
+    """bfloat16 / batched entry points: operands resident in HBM, CUDA events on the launching stream."""
+    import torch
+
+    entry.load_package()
+    from cudanative_jl_b200 import _lib, rng
+    from cudanative_jl_b200.bfloat16 import BFloat16
+    from cudanative_jl_b200.gemm import Handle
+
+    if int(os.environ.get("WORLD_SIZE", "1")) != 1:
+        raise SystemExit(f"workload {args.workload} runs on one GPU")
+    w = EXTRA_WORKLOADS[args.workload]
+    M, N, K, batch = w["M"], w["N"], w["K"], w["batch"]
+    torch.cuda.set_device(0)
+    h = Handle(0)
+    stream = torch.cuda.current_stream().cuda_stream
+    peaks = measured_peaks()
+    L = _lib.lib()
+    a_rows, a_cols = (K, M) if w["transA"] else (M, K)
+    A = torch.empty(batch * M * K, dtype=torch.float16, device="cuda")  # 16-bit storage for either operand type
+    B = torch.empty(batch * K * N, dtype=torch.float16, device="cuda")
+    Cm = torch.empty(batch * M * N, dtype=torch.float32, device="cuda")
+    D = torch.empty(batch * M * N, dtype=torch.float32, device="cuda")
+    fill16 = L.b200_fill_bf16 if w["bf16"] else L.b200_fill_f16
+    # a batch is laid out as one tall synthetic matrix per operand: matrix i = columns [i*cols, (i+1)*cols)
+    _lib.check(fill16(stream, A.data_ptr(), a_rows, a_cols * batch, a_rows, w["seed"], 0, 0, rng.NORMAL, K ** -0.5), "fill")
+    _lib.check(fill16(stream, B.data_ptr(), K, N * batch, K, w["seed"], 1, 0, rng.NORMAL, K ** -0.5), "fill")
+    _lib.check(L.b200_fill_f32(stream, Cm.data_ptr(), M, N * batch, M, w["seed"], 2, 0, rng.UNIFORM, 1.0), "fill")
+    ab = BFloat16 if w["bf16"] else np.float16
+
+    def step():
+        h.gemm_strided_batched(w["transA"], w["transB"], M, N, K, w["alpha"], A.data_ptr(), a_rows, M * K, B.data_ptr(), K,
+                               K * N, ab, w["beta"], Cm.data_ptr(), M, M * N, np.float32, D.data_ptr(), M, M * N,
+                               np.float32, batch, stream=stream)
+
+    def loop_step():  # the same work as one launch per matrix
+        for i in range(batch):
+            h.gemm(w["transA"], w["transB"], M, N, K, w["alpha"], A.data_ptr() + 2 * i * M * K, a_rows,
+                   B.data_ptr() + 2 * i * K * N, K, w["beta"], Cm.data_ptr() + 4 * i * M * N, M, D.data_ptr() + 4 * i * M * N,
+                   M, stream=stream)
+
+    def timed(fn, steps):
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        torch.cuda.synchronize()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        for _ in range(steps):
+            fn()
+        ev1.record()
+        torch.cuda.synchronize()
+        code, block, _ = h.device_status()
+        if code:
+            raise SystemExit(f"device wait {code} ran out in block {block}")
+        return ev0.elapsed_time(ev1), ev0.elapsed_time(ev1) / steps
+
+    sampler = ClockSampler(0)
+    sampler.start()
+    time.sleep(0.25)
+    t0 = time.perf_counter()
+    ms_total, ms_step = timed(step, args.steps)
+    t1 = time.perf_counter()
+    clocks = sampler.stop(t0, t1)
+    launch = h.last_launch()
+    flops = 2.0 * M * N * K * batch
+    tflops = flops / (ms_step * 1e-3) / 1e12
+    nbytes = batch * (2 * M * K + 2 * K * N + 8 * M * N)
+    long_run = ms_total * 1e-3 > 1.0
+    peak = peaks["tf_sustained"] if long_run else peaks["tf_burst"]
+    out = {
+        "metric": METRIC, "value": round(tflops, 2), "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": round(ms_step, 5), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16*bf16->f32" if w["bf16"] else "f16*f16->f32", "data": "synthetic",
+        "config": {"workload": args.workload, "M": M, "N": N, "K": K, "batch": batch, "transA": w["transA"],
+                   "transB": w["transB"], "alpha": w["alpha"], "beta": w["beta"], "seed": w["seed"], "kernel": launch,
+                   "l2": f"inputs+outputs {nbytes / 1e6:.0f} MB per step exceed the 126 MB L2; no flush"},
+        "clocks": clocks, "e2e": None, "gpu_launches": args.steps,
+        "roofline": {"bound": "tensor", "achieved": round(tflops, 2), "peak": peak, "unit": "TFLOP/s",
+                     "frac": round(tflops / peak, 4), "traffic": None,
+                     "peak_source": f"{peaks['source']} ({'bf16_tflops_sustained' if long_run else 'bf16_tflops'})",
+                     "hbm_gbs_algorithmic": round(nbytes / (ms_step * 1e-3) / 1e9, 1), "hbm_peak_gbs": peaks["hbm_gbs"]},
+    }
+    if batch > 1:
+        _, loop_ms = timed(loop_step, max(1, args.steps // 4))
+        out["one_launch_per_matrix"] = {"ms_per_step": round(loop_ms, 5), "value": round(flops / (loop_ms * 1e-3) / 1e12, 2),
+                                        "unit": "TFLOP/s", "gpu_launches_per_step": batch}
+    print(json.dumps(out), flush=True)
+
+
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures summarised in
 # profiles/gemm8192_tcgen05_pair_256x256.md and profiles/skinny_tcgen05_128x128.md
 NCU_TRAFFIC = {"gemm8192": 1465122000 + 253011200, "skinny": 270598912 + 4099840}
@@ -476,7 +574,7 @@ def main():
     ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS) + sorted(EXTRA_WORKLOADS))
     ap.add_argument("--panels", type=int, default=16, help="K panels in which A travels (sharded)")
     ap.add_argument("--nccl-ctas", type=int, default=8, help="SMs left to NCCL while a broadcast is in flight (transport nccl)")
     ap.add_argument("--gated", action="store_true", help="p2p transport: one gated GEMM launch instead of a few launches over growing K ranges")
@@ -485,7 +583,11 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-scaling-baseline", action="store_true", help="N=1: skip the one-GPU run of the sharded workload")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.workload in EXTRA_WORKLOADS:
+        if args.impl == "reference":
+            raise SystemExit(f"workload {args.workload} has no CPU leg")
+        run_extra(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

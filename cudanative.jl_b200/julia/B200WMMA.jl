@@ -157,6 +157,31 @@ function gemm!(h::Handle, D, A, B, C = nothing; alpha = 1f0, beta = 0f0, transA 
                 C === nothing ? CuPtr{Cvoid}(0) : C.ptr, C === nothing ? M : C.ld, D.ptr, D.ld))
 end
 
+# element tags of include/b200wmma.h; bfloat16 data is passed as 16-bit words (e.g. CuPtr{UInt16})
+const ELEM_F16, ELEM_F32, ELEM_BF16 = Cint(0), Cint(1), Cint(2)
+
+"""
+    gemm_strided_batched!(h, D, A, B, C; batch, ab_type, c_type, d_type, alpha, beta, transA, transB, stream)
+
+`batch` products of one shape in one call (b200_gemm_strided_batched).  Operands are named tuples
+(ptr, rows, cols, ld, stride): matrix i starts `stride * i` elements after `ptr`; a stride of 0 repeats
+A, B or C.  `ab_type` is ELEM_F16 or ELEM_BF16, `c_type` / `d_type` any of the three tags.
+`batch = 1` is b200_gemm_ex: one product with bfloat16 operands and / or 16-bit C and D.
+"""
+function gemm_strided_batched!(h::Handle, D, A, B, C = nothing; batch = 1, ab_type = ELEM_F16, c_type = ELEM_F32,
+                               d_type = ELEM_F32, alpha = 1f0, beta = 0f0, transA = false, transB = false,
+                               stream::CuStream = CuDefaultStream())
+    M, K = transA ? (A.cols, A.rows) : (A.rows, A.cols)
+    N = transB ? B.rows : B.cols
+    check(ccall((:b200_gemm_strided_batched, lib), Cint,
+                (Ptr{Cvoid}, Ptr{Cvoid}, Cint, Cint, Int64, Int64, Int64, Cfloat, CuPtr{Cvoid}, Int64, Int64,
+                 CuPtr{Cvoid}, Int64, Int64, Cint, Cfloat, CuPtr{Cvoid}, Int64, Int64, Cint, CuPtr{Cvoid}, Int64, Int64,
+                 Cint, Int64),
+                h.ptr, stream.handle, transA, transB, M, N, K, alpha, A.ptr, A.ld, A.stride, B.ptr, B.ld, B.stride,
+                ab_type, beta, C === nothing ? CuPtr{Cvoid}(0) : C.ptr, C === nothing ? M : C.ld,
+                C === nothing ? 0 : C.stride, c_type, D.ptr, D.ld, D.stride, d_type, batch))
+end
+
 "Host-buffer form: `Array`s in, `Array` out, copies inside (b200_gemm_f16f32_host)."
 function gemm_host!(h::Handle, D::Matrix{Float32}, A::Matrix{Float16}, B::Matrix{Float16},
                     C::Union{Matrix{Float32}, Nothing} = nothing; alpha = 1f0, beta = 0f0, transA = false, transB = false)
