@@ -41,6 +41,8 @@ class DevicePtr:
             return obj
         if isinstance(obj, CuHostArray):
             return DevicePtr(obj.dtype, obj.ptr, obj)
+        if isinstance(getattr(obj, "ptr", None), DevicePtr):  # a converted kernel argument (execution.CuDeviceArray)
+            return obj.ptr
         if hasattr(obj, "data_ptr") and hasattr(obj, "is_cuda"):
             if not obj.is_cuda:
                 raise TypeError("expected a CUDA tensor")

@@ -33,6 +33,7 @@ import numpy as np
 
 from . import _lib
 from .array import CuHostArray, DevicePtr, Float16, Float32, pointer  # noqa: F401
+from .execution import current_stream, require_full_warp
 
 
 # ---- layouts, uses ---------------------------------------------------------------------------
@@ -192,8 +193,9 @@ class Fragment:
             s = self.T.type(scalar)
             f = (lambda v: self.T.type(s * v)) if op == 0 else (lambda v: self.T.type(s + v))
             return self._like(tuple(f(v) for v in self.values))
+        require_full_warp("fragment broadcast")
         out = CuHostArray(self.T, shape=(32 * self.FS,))
-        _lib.check(_lib.lib().b200_wmma_bcast(None, op, _TYPE_CODE[self.T], self.FS, float(scalar),
+        _lib.check(_lib.lib().b200_wmma_bcast(current_stream(), op, _TYPE_CODE[self.T], self.FS, float(scalar),
                                               self.buf.ptr, out.ptr), "broadcast")
         return self._like(out)
 
@@ -218,8 +220,9 @@ def _load(matrix: str, addr, stride, layout, config: Config) -> Fragment:
     addr = DevicePtr.of(addr)
     code = _layout_code(layout)
     _check_shape(config)
+    require_full_warp(f"load_{matrix}")
     frag = _new_frag(matrix, addr.dtype, Unspecified if matrix == "c" else layout, config)
-    _lib.check(_lib.lib().b200_wmma_load(None, _USE_CODE[frag.U], code, _TYPE_CODE[addr.dtype], addr.addr,
+    _lib.check(_lib.lib().b200_wmma_load(current_stream(), _USE_CODE[frag.U], code, _TYPE_CODE[addr.dtype], addr.addr,
                                          int(stride), frag.buf.ptr), f"load_{matrix}")
     return frag
 
@@ -243,8 +246,9 @@ def fill_c(value, config: Config) -> Fragment:
     """A ``c`` fragment filled with ``value`` (a numpy float16 / float32 scalar picks the type)."""
     T = np.dtype(type(value)) if isinstance(value, np.generic) else np.dtype(np.float32)
     _check_shape(config)
+    require_full_warp("fill_c")
     frag = _new_frag("c", T, Unspecified, config)
-    _lib.check(_lib.lib().b200_wmma_fill_c(None, _TYPE_CODE[frag.T], float(value), frag.buf.ptr), "fill_c")
+    _lib.check(_lib.lib().b200_wmma_fill_c(current_stream(), _TYPE_CODE[frag.T], float(value), frag.buf.ptr), "fill_c")
     return frag
 
 
@@ -261,8 +265,9 @@ def mma(a: Fragment, b: Fragment, c: Fragment, config: Config) -> Fragment:
             raise TypeError("mma needs device fragments (from load_* or fill_c)")
     _check_shape(config)
     _layout_code(a.L), _layout_code(b.L)
+    require_full_warp("mma")
     d = _new_frag("d", config.d_type, Unspecified, config)
-    _lib.check(_lib.lib().b200_wmma_mma(None, _TYPE_CODE[c.T], _TYPE_CODE[d.T], a.buf.ptr, b.buf.ptr,
+    _lib.check(_lib.lib().b200_wmma_mma(current_stream(), _TYPE_CODE[c.T], _TYPE_CODE[d.T], a.buf.ptr, b.buf.ptr,
                                         c.buf.ptr, d.buf.ptr), "mma")
     return d
 
@@ -276,8 +281,80 @@ def store_d(addr, d: Fragment, stride, layout, config: Config) -> None:
         raise TypeError("store_d: pointer, fragment and Config element types must agree")
     code = _layout_code(layout)
     _check_shape(config)
-    _lib.check(_lib.lib().b200_wmma_store_d(None, code, _TYPE_CODE[d.T], addr.addr, d.buf.ptr, int(stride)),
+    require_full_warp("store_d")
+    _lib.check(_lib.lib().b200_wmma_store_d(current_stream(), code, _TYPE_CODE[d.T], addr.addr, d.buf.ptr, int(stride)),
                "store_d")
+
+
+# ---- the low-level wrappers (wmma.jl:104-257) under their reference names ------------------------
+# 24 loads, 12 stores, 16 multiply-accumulates, e.g. llvm_wmma_load_a_col_m16n16k16_stride_f16(addr, stride),
+# llvm_wmma_mma_col_col_m16n16k16_f32_f32(a, b, c), llvm_wmma_store_d_col_m16n16k16_stride_f32(addr, d, stride).
+# In the reference they move per-thread register tuples; here they move Fragments, like the high-level API
+# they back.  The `_global` forms take the same pointers as the generic ones.  The `_shared` forms need a
+# shared-memory address, which only device code has: they exist (so that a script naming them imports) and
+# refuse the call; the linkable device library carries the real ones.
+_ELT = {"f16": np.dtype(np.float16), "f32": np.dtype(np.float32)}
+_LAYOUT_OF = {"col": ColMajor, "row": RowMajor}
+LLVM_WRAPPERS: list = []
+
+
+def _define_llvm_wrappers() -> None:
+    unit = Config(16, 16, 16, np.float32)
+
+    def shared_refusal(name):
+        def fn(*_args):
+            raise _lib.B200Error(_lib.UNSUPPORTED, f"{name}: a shared-memory address exists only in device code; "
+                                                   f"link b200_{name[5:]} from the device library instead")
+        return fn
+
+    def check_ptr(name, addr, elt):
+        addr = DevicePtr.of(addr)
+        if addr.dtype != _ELT[elt]:
+            raise TypeError(f"{name}: expected a pointer to {_ELT[elt].name}, got {addr.dtype.name}")
+        return addr
+
+    def make_load(name, mat, layout, elt):
+        def fn(src_addr, stride):
+            return _load(mat, check_ptr(name, src_addr, elt), stride, _LAYOUT_OF[layout], unit)
+        return fn
+
+    def make_store(name, layout, elt):
+        def fn(dst_addr, data, stride):
+            return store_d(check_ptr(name, dst_addr, elt), data, stride, _LAYOUT_OF[layout], Config(16, 16, 16, _ELT[elt]))
+        return fn
+
+    def make_mma(name, a_layout, b_layout, d_elt, c_elt):
+        def fn(a, b, c):
+            if isinstance(a, Fragment) and isinstance(b, Fragment) and (a.L is not _LAYOUT_OF[a_layout] or b.L is not _LAYOUT_OF[b_layout]):
+                raise TypeError(f"{name}: fragments were loaded as {a.L.__name__} / {b.L.__name__}")
+            if isinstance(c, Fragment) and c.T != _ELT[c_elt]:
+                raise TypeError(f"{name}: expected a {_ELT[c_elt].name} accumulator")
+            return mma(a, b, c, Config(16, 16, 16, _ELT[d_elt]))
+        return fn
+
+    table = {}
+    for space in ("", "_global", "_shared"):
+        for layout in ("col", "row"):
+            for mat, elts in (("a", ("f16",)), ("b", ("f16",)), ("c", ("f16", "f32"))):
+                for elt in elts:
+                    name = f"llvm_wmma_load_{mat}_{layout}_m16n16k16{space}_stride_{elt}"
+                    table[name] = shared_refusal(name) if space == "_shared" else make_load(name, mat, layout, elt)
+            for elt in ("f16", "f32"):
+                name = f"llvm_wmma_store_d_{layout}_m16n16k16{space}_stride_{elt}"
+                table[name] = shared_refusal(name) if space == "_shared" else make_store(name, layout, elt)
+    for a_layout in ("col", "row"):
+        for b_layout in ("col", "row"):
+            for d_elt in ("f16", "f32"):
+                for c_elt in ("f16", "f32"):
+                    name = f"llvm_wmma_mma_{a_layout}_{b_layout}_m16n16k16_{d_elt}_{c_elt}"
+                    table[name] = make_mma(name, a_layout, b_layout, d_elt, c_elt)
+    for name, fn in table.items():
+        fn.__name__ = fn.__qualname__ = name
+        globals()[name] = fn
+        LLVM_WRAPPERS.append(name)
+
+
+_define_llvm_wrappers()
 
 
 def synchronize() -> None:
