@@ -124,10 +124,22 @@ GemmPlan make_plan(const b200_handle* h, const GemmProblem& g) {
     return plan;
 }
 
+// The handle's status word and scratch live on its device and the launch goes to the calling
+// thread's current device: the two must be the same.
+int check_current_device(const b200_handle* h) {
+    int cur = -1;
+    B200_CUDA_TRY(cudaGetDevice(&cur));
+    if (cur != h->device)
+        return fail(B200_INVALID_ARG, "the handle belongs to device " + std::to_string(h->device) +
+                                          " but the calling thread's current device is " + std::to_string(cur));
+    return B200_OK;
+}
+
 int run_gemm(b200_handle* h, cudaStream_t stream, const GemmProblem& g) {
     int rc = validate(g);
     if (rc) return rc;
     if (g.M == 0 || g.N == 0 || g.batch == 0) return B200_OK;
+    if ((rc = check_current_device(h))) return rc;
     std::string why;
     const bool eligible = gemm_tcgen05_eligible(g, &why);
     int kernel = h->force_kernel;
@@ -335,6 +347,7 @@ int b200_device_status(b200_handle* h, int* code, int* block, int* detail) {
 int b200_selftest_bounded_wait(b200_handle* h, b200_stream stream, int64_t budget_ns) {
     if (!h) return fail(B200_INVALID_ARG, "null handle");
     if (budget_ns < 1000 || budget_ns > 1000000000ll) return fail(B200_INVALID_ARG, "selftest budget must be within [1 us, 1 s]");
+    if (int rc = check_current_device(h)) return rc;
     bounded_wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(h->status_word, static_cast<unsigned long long>(budget_ns));
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;

@@ -87,8 +87,11 @@ int b200_version(void);
 int b200_device_count(void);
 
 /* Create / destroy the per-device handle: device status word, workspace for the host-buffer
- * entry point, tensor-map cache.  Binds to the device's primary context, the one CUDAnative's
- * device!() uses (src/init.jl:187-209).  One handle per host thread (or lock externally). */
+ * entry point, split-K scratch.  Binds to the device's primary context and makes `device` the
+ * calling thread's current device, as CUDAnative's device!() does (src/init.jl:187-209).  One
+ * handle per host thread (or lock externally).  The entry points that take a handle and a stream
+ * launch on the calling thread's current device; they return B200_INVALID_ARG when that is not
+ * the handle's device. */
 int b200_create(b200_handle** out, int device);
 int b200_destroy(b200_handle* h);
 

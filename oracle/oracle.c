@@ -77,6 +77,37 @@ float oracle_f16_bits_to_f32(uint16_t h) {
 
 float oracle_round_f16(float f) { return oracle_f16_bits_to_f32(oracle_f32_to_f16_bits(f)); }
 
+/* ---- bfloat16 <-> binary32 ---------------------------------------------------------------
+ * bfloat16 is the upper half of a binary32 (1 sign, 8 exponent, 7 fraction bits); the reference has no
+ * such type (its WMMA element types are Float16 and Float32, src/device/cuda/wmma.jl:11-37), so this
+ * follows IEEE 754 round-to-nearest-even on the dropped 16 bits.  Written with a comparison of the
+ * remainder against the half-way point instead of the add-and-shift trick the library's host helper
+ * uses, so that the two check each other. */
+uint16_t oracle_f32_to_bf16_bits(float f) {
+    uint32_t x;
+    memcpy(&x, &f, 4);
+    if ((x & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((x >> 16) | 0x0040u); /* NaN stays NaN (quiet) */
+    uint32_t kept = x >> 16;
+    const uint32_t rem = x & 0xffffu;
+    if (rem > 0x8000u || (rem == 0x8000u && (kept & 1u))) kept++; /* may carry into the exponent: up to infinity */
+    return (uint16_t)kept;
+}
+
+float oracle_bf16_bits_to_f32(uint16_t b) {
+    const uint32_t x = (uint32_t)b << 16;
+    float f;
+    memcpy(&f, &x, 4);
+    return f;
+}
+
+void oracle_round_bf16_array(const float* in, uint16_t* out, int64_t n) {
+    for (int64_t i = 0; i < n; ++i) out[i] = oracle_f32_to_bf16_bits(in[i]);
+}
+
+void oracle_widen_bf16_array(const uint16_t* in, float* out, int64_t n) {
+    for (int64_t i = 0; i < n; ++i) out[i] = oracle_bf16_bits_to_f32(in[i]);
+}
+
 /* ---- counter-based inputs (same definition as the library's fill kernels) ---------------- */
 static uint64_t splitmix64(uint64_t x) {
     x += 0x9E3779B97F4A7C15ull;

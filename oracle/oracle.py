@@ -56,6 +56,11 @@ def clib() -> C.CDLL:
         L.oracle_f16_bits_to_f32.argtypes = [C.c_uint16]
         L.oracle_round_f16.restype = C.c_float
         L.oracle_round_f16.argtypes = [C.c_float]
+        u16p = C.POINTER(C.c_uint16)
+        L.oracle_round_bf16_array.restype = None
+        L.oracle_round_bf16_array.argtypes = [fp, u16p, C.c_int64]
+        L.oracle_widen_bf16_array.restype = None
+        L.oracle_widen_bf16_array.argtypes = [u16p, fp, C.c_int64]
         L.oracle_synth_value.restype = C.c_float
         L.oracle_synth_value.argtypes = [C.c_uint64, C.c_uint64, C.c_uint64, C.c_int]
         L.oracle_fill.restype = None
@@ -80,6 +85,24 @@ def fill(rows: int, cols: int, seed: int, matrix_id: int, dist: int, scale: floa
     ``f16`` rounds the values to binary16 (they stay stored as float32)."""
     out = np.empty((rows, cols), dtype=np.float32, order="F")
     clib().oracle_fill(_fptr(out), rows, cols, rows, seed, matrix_id, col0, dist, scale, int(f16))
+    return out
+
+
+def bf16_round(x: np.ndarray) -> np.ndarray:
+    """float32 array -> bfloat16 bit patterns (uint16, same shape and memory order), round to nearest even."""
+    order = "F" if x.flags.f_contiguous and not x.flags.c_contiguous else "C"
+    src = np.array(x, dtype=np.float32, order=order)
+    out = np.empty(src.shape, dtype=np.uint16, order=order)
+    clib().oracle_round_bf16_array(_fptr(src), out.ctypes.data_as(C.POINTER(C.c_uint16)), src.size)
+    return out
+
+
+def bf16_widen(bits: np.ndarray) -> np.ndarray:
+    """bfloat16 bit patterns (uint16) -> the float32 values they stand for."""
+    order = "F" if bits.flags.f_contiguous and not bits.flags.c_contiguous else "C"
+    src = np.array(bits, dtype=np.uint16, order=order)
+    out = np.empty(src.shape, dtype=np.float32, order=order)
+    clib().oracle_widen_bf16_array(src.ctypes.data_as(C.POINTER(C.c_uint16)), _fptr(out), src.size)
     return out
 
 

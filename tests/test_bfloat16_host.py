@@ -47,3 +47,18 @@ def test_type_tags():
     assert _type_code(BFloat16) == _lib.BF16 == 2
     with pytest.raises(TypeError):
         _type_code(np.float64)
+
+
+def test_library_helpers_agree_with_the_oracle(oracle):
+    """The oracle rounds by comparing the dropped bits with the half-way point, the library's helper by
+    add-and-shift: two statements of round-to-nearest-even that must give the same bits."""
+    rand = np.random.default_rng(11)
+    x = (rand.standard_normal(20000) * 10.0 ** rand.integers(-30, 30, 20000)).astype(np.float32)
+    ties = (np.arange(0x3F80, 0x3F80 + 512, dtype=np.uint32) << 16 | 0x8000).view(np.float32)  # exact half-way cases
+    special = np.array([0.0, -0.0, np.inf, -np.inf, 3.3895314e38, 3.4e38, -3.4e38, 1e-40, -1e-45], dtype=np.float32)
+    for arr in (x, ties, special, np.asfortranarray(x[:600].reshape(20, 30))):
+        assert np.array_equal(round_to_bf16(arr), oracle.bf16_round(arr))
+        bits = oracle.bf16_round(arr)
+        assert np.array_equal(widen_bf16(bits), oracle.bf16_widen(bits))
+    nan = oracle.bf16_round(np.array([np.nan, -np.nan], dtype=np.float32))
+    assert np.all(np.isnan(oracle.bf16_widen(nan)))

@@ -32,10 +32,11 @@ def store(values32: np.ndarray, elem) -> np.ndarray:
     return values32.astype(elem)
 
 
-def value(stored: np.ndarray, elem) -> np.ndarray:
-    """stored array -> the float32 values it stands for."""
+def value(stored: np.ndarray, elem, oracle) -> np.ndarray:
+    """stored array -> the float32 values it stands for (bfloat16 through the oracle's own conversion,
+    not the library's host helper that prepared the inputs)."""
     if elem is BFloat16:
-        return widen_bf16(stored)
+        return oracle.bf16_widen(stored)
     return stored.astype(np.float32)
 
 
@@ -120,14 +121,15 @@ def run_batch(handle, oracle, tA, tB, M, N, K, batch, *, ab=np.float16, c_type=n
             written[i * sd + j * ldd: i * sd + j * ldd + M] = True
     assert np.all(flat[~written] == sent), "wrote outside the D matrices"
     for i, (a, b, c) in enumerate(probs):
-        ref = oracle.gemm_ref(tA, tB, alpha, value(a, ab), value(b, ab), beta, value(c, c_type) if beta != 0.0 else None)
-        d = value(got[i], d_type)
+        ref = oracle.gemm_ref(tA, tB, alpha, value(a, ab, oracle), value(b, ab, oracle), beta,
+                              value(c, c_type, oracle) if beta != 0.0 else None)
+        d = value(got[i], d_type, oracle)
         if d_type is BFloat16:
             # One rounding to nearest even on the way out.  Half an ulp of 8 significant bits is 2e-3
             # of the value, more than the acceptance allows in the Frobenius norm, so the yardstick is
             # the oracle's result rounded the same way: equal except where the two binary32 results
             # straddle a rounding boundary (one ulp).
-            ref_rounded = widen_bf16(round_to_bf16(ref))
+            ref_rounded = oracle.bf16_widen(oracle.bf16_round(ref))
             assert np.max(np.abs(d - ref_rounded) / (np.abs(ref) + 1)) <= 2.0 ** -7
             ref = ref_rounded
         oracle.assert_close(d, ref, f"matrix {i} of {batch}: tA={tA} tB={tB} {M}x{N}x{K}")
@@ -151,7 +153,8 @@ def test_bfloat16_operands(handle, oracle, kernel, tA, tB):
     d = Array(d_dev)
     assert handle.device_status()[0] == 0
     assert handle.last_launch()["kernel"] == kernel
-    oracle.assert_close(d, oracle.gemm_ref(tA, tB, 2.0 ** -20, widen_bf16(a), widen_bf16(b), 0.5, c), f"bf16 tA={tA} tB={tB}")
+    oracle.assert_close(d, oracle.gemm_ref(tA, tB, 2.0 ** -20, oracle.bf16_widen(a), oracle.bf16_widen(b), 0.5, c),
+                        f"bf16 tA={tA} tB={tB}")
 
 
 @pytest.mark.parametrize("tile_n,pair,split_k", [(256, 2, 0), (128, 1, 0), (64, 1, 0), (256, 1, 3), (128, 2, 2)])

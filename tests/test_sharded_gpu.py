@@ -25,3 +25,27 @@ def test_sharded_gemm_two_gpus(lib, shape, panels, transport):
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=240, env=env)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert r.stdout.count(" ok: slab") == 2
+
+
+def test_handle_is_refused_on_another_current_device(lib, pkg):
+    """A handle's status word and scratch live on its device, a launch goes to the calling thread's current
+    device: the GEMM entry points refuse the call when the two differ instead of launching on the wrong GPU."""
+    if gpu_count(lib) < 2:
+        pytest.skip("needs two GPUs")
+    import numpy as np
+
+    from cudanative_jl_b200 import B200Error
+    from cudanative_jl_b200.array import CuArray
+    from cudanative_jl_b200.gemm import Handle
+
+    h0 = Handle(0)
+    buf = CuArray(np.zeros((64, 64), dtype=np.float16, order="F"))
+    out = CuArray(np.zeros((64, 64), dtype=np.float32, order="F"))
+    h1 = Handle(1)  # like device!(1): device 1 is now the calling thread's current device
+    try:
+        with pytest.raises(B200Error, match="belongs to device 0 but the calling thread's current device is 1"):
+            h0.gemm(False, False, 64, 64, 64, 1.0, buf, 64, buf, 64, 0.0, None, 64, out, 64)
+    finally:
+        h1.close()
+        Handle(0).close()  # back to device 0 for the tests that follow
+        h0.close()
