@@ -48,10 +48,18 @@ use_code(::Type{MatrixB}) = Cint(1)
 use_code(::Type{Accumulator}) = Cint(2)
 check_shape(M, N, K) = (M, N, K) == (16, 16, 16) || error("Invalid shape for WMMA: (M, N, K) = ($M, $N, $K)")
 
-# A fragment is the whole warp's register image in device memory: 32 lanes x FS elements.
-struct Fragment{M, N, K, FS, T, L <: FragmentLayout, U <: FragmentUse}
+# A fragment is the whole warp's register image in device memory: 32 lanes x FS elements.  It owns that
+# memory (allocated by alloc_fragment) and gives it back when the garbage collector drops it, as the
+# reference's CuHostArray does (src/array.jl:33-35).
+mutable struct Fragment{M, N, K, FS, T, L <: FragmentLayout, U <: FragmentUse}
     x::CuPtr{T}
+    function Fragment{M, N, K, FS, T, L, U}(x::CuPtr{T}) where {M, N, K, FS, T, L <: FragmentLayout, U <: FragmentUse}
+        f = new{M, N, K, FS, T, L, U}(x)
+        finalizer(free_fragment, f)
+        return f
+    end
 end
+free_fragment(f::Fragment) = ccall((:b200_free, lib), Cint, (CuPtr{Cvoid},), f.x)
 
 num_elems(::Type{MatrixA}) = 16
 num_elems(::Type{MatrixB}) = 16
@@ -138,6 +146,22 @@ mutable struct Handle
         finalizer(x -> ccall((:b200_destroy, lib), Cint, (Ptr{Cvoid},), x.ptr), h)
         return h
     end
+end
+
+"Set one of the B200_OPT_* options of include/b200wmma.h (kernel choice, tile width, split-K, wait budget ...)."
+set_option!(h::Handle, option::Integer, value::Integer) =
+    check(ccall((:b200_set_option, lib), Cint, (Ptr{Cvoid}, Cint, Int64), h.ptr, option, value))
+
+"""
+    device_status(h) -> (code, block, detail)
+
+Reads (and clears) the device status word after a synchronisation: `code == 0` means no bounded wait inside a
+kernel ran out -- the role of the reference's exception flag check (src/exceptions.jl:76-89).
+"""
+function device_status(h::Handle)
+    code, block, detail = Ref{Cint}(0), Ref{Cint}(0), Ref{Cint}(0)
+    check(ccall((:b200_device_status, lib), Cint, (Ptr{Cvoid}, Ptr{Cint}, Ptr{Cint}, Ptr{Cint}), h.ptr, code, block, detail))
+    return (code[], block[], detail[])
 end
 
 """
