@@ -3,7 +3,7 @@
 TEST INFRASTRUCTURE ONLY: imported by tests/, by ``__graft_entry__.smoke()`` and by the CPU legs of
 ``bench.py``; never by the product package.  PARITY UNPINNED for the arithmetic (see oracle.c): the
 reference delegates D = A*B + C to the wmma.mma instruction, has no golden vectors, and cannot be run
-here (no Julia), so BASELINE tolerances are the contract.
+here (no Julia), so the benchmark specification's tolerances are the contract.
 
 Two statements of the same product are kept side by side and checked against each other:
 
@@ -27,7 +27,7 @@ import numpy as np
 HERE = Path(__file__).resolve().parent
 LIB = HERE / "liboracle.so"
 
-# BASELINE tolerances for the tiled GEMM
+# the benchmark specification's tolerances for the tiled GEMM
 REL_FRO_TOL = 1e-3
 ELEM_TOL = 1e-2
 # the reference's own tolerance for the 16x16x16 unit: rtol = sqrt(eps(Float16))
@@ -150,7 +150,7 @@ def errors(D: np.ndarray, ref: np.ndarray) -> tuple[float, float]:
 
 
 def assert_close(D: np.ndarray, ref: np.ndarray, what: str = "") -> tuple[float, float]:
-    """BASELINE acceptance: rel-Frobenius <= 1e-3 and |D-ref| <= 1e-2*(|ref|+1) elementwise."""
+    """Acceptance of the benchmark specification: rel-Frobenius <= 1e-3 and |D-ref| <= 1e-2*(|ref|+1) elementwise."""
     assert D.shape == ref.shape, f"{what}: shape {D.shape} vs {ref.shape}"
     assert np.all(np.isfinite(D)), f"{what}: non-finite output"
     rel, elem = errors(D, ref)

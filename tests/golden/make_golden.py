@@ -5,7 +5,7 @@
 The reference (CUDAnative.jl) has no stored vectors for this path and cannot be run without Julia, so
 these fixtures pin the three statements of the same arithmetic against each other instead: the C
 oracle (oracle/oracle.c), its numpy front end (oracle/oracle.py) and the library's generator
-(cudanative.jl_b200/rng.py; csrc/rng.cuh on the device).  Inputs are the BASELINE configurations'
+(cudanative.jl_b200/rng.py; csrc/rng.cuh on the device).  Inputs are the benchmark configurations'
 own seeds and distributions, cut down to sizes a CPU test handles in milliseconds.
 """
 import sys
@@ -31,7 +31,7 @@ def main():
             for dist, name in ((rng.UNIFORM, "u"), (rng.NORMAL, "n")):
                 kat[f"s{seed}_m{mid}_{name}"] = rng.synth_values(seed, mid, np.arange(16, dtype=np.uint64) * np.uint64(1000003), dist)
     np.savez(HERE / "rng_kat.npz", **kat)
-    # 2. BASELINE config 1: 16x16x16, uniform[-1,1), seed 0, D = A*B + C
+    # 2. benchmark config 1: 16x16x16, uniform[-1,1), seed 0, D = A*B + C
     a = rng.matrix(0, 0, 16, 16, rng.UNIFORM, 1.0, np.float16)
     b = rng.matrix(0, 1, 16, 16, rng.UNIFORM, 1.0, np.float16)
     c = rng.matrix(0, 2, 16, 16, rng.UNIFORM, 1.0, np.float32)

@@ -1,6 +1,6 @@
 """Parity of the tiled GEMM (through the C ABI) with the CPU oracle.
 
-Tolerances are BASELINE's: relative Frobenius error <= 1e-3 and |D - ref| <= 1e-2 * (|ref| + 1)
+Tolerances are the benchmark specification's: relative Frobenius error <= 1e-3 and |D - ref| <= 1e-2 * (|ref| + 1)
 elementwise, against float32 sgemm on the Float16-rounded inputs (oracle.assert_close)."""
 import numpy as np
 import pytest
@@ -219,7 +219,7 @@ def test_deterministic(handle):
 
 
 def test_config2_4096_cubed(handle, oracle):
-    """BASELINE config 2: M=N=K=4096, A, B column-major normal/sqrt(K), C normal, alpha=beta=1, seed 1."""
+    """Benchmark config 2: M=N=K=4096, A, B column-major normal/sqrt(K), C normal, alpha=beta=1, seed 1."""
     force(handle, _lib.KERNEL_AUTO)
     n = 4096
     a = rng.matrix(1, 0, n, n, rng.NORMAL, n ** -0.5, np.float16)
@@ -231,7 +231,7 @@ def test_config2_4096_cubed(handle, oracle):
 
 
 def test_config4_skinny(handle, oracle):
-    """BASELINE config 4: M=16384, N=128, K=8192, A column-major normal/sqrt(K), B normal, C zeros, beta=0, seed 3."""
+    """Benchmark config 4: M=16384, N=128, K=8192, A column-major normal/sqrt(K), B normal, C zeros, beta=0, seed 3."""
     force(handle, _lib.KERNEL_AUTO)
     M, N, K = 16384, 128, 8192
     a = rng.matrix(3, 0, M, K, rng.NORMAL, K ** -0.5, np.float16)
@@ -253,7 +253,7 @@ def _device_problem(handle, M, N, K, seed, transA, c_dist):
 
 
 def test_config3_8192_cubed_properties(handle, oracle):
-    """BASELINE config 3 at full size: A row-major, B column-major, alpha=2, beta=0.5, seed 2.
+    """Benchmark config 3 at full size: A row-major, B column-major, alpha=2, beta=0.5, seed 2.
     Checked three ways without a full CPU product: (1) against the independent plain kernel on
     the device, elementwise over the whole matrix; (2) sampled 128x128 tiles against the CPU
     oracle with operands regenerated from the counter-based generator; (3) linearity in alpha."""

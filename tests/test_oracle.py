@@ -3,7 +3,7 @@
 The reference has no golden vectors for this path (its tests recompute a CPU product from unseeded
 rand(), test/device/wmma.jl:102-151 of CUDAnative.jl), so what is pinned here is that the three
 statements of the arithmetic -- oracle.c, numpy/OpenBLAS sgemm, and a float64 triple loop -- agree,
-and that they still produce the committed outputs for the BASELINE seeds."""
+and that they still produce the committed outputs for the benchmark configurations' seeds."""
 from pathlib import Path
 
 import numpy as np

@@ -98,7 +98,7 @@ def test_fragment_api_128_case_sweep(oracle):
 
 @pytest.mark.parametrize("lowering", [wmma.LOWER_WARP, wmma.LOWER_TCGEN05])
 def test_config1_and_example(oracle, lowering):
-    """BASELINE config 1 (uniform[-1,1), seed 0, D = A*B + C) and the reference's example
+    """Benchmark config 1 (uniform[-1,1), seed 0, D = A*B + C) and the reference's example
     (examples/wmma/high-level.jl:49: a*b + 0.5*c with rtol 0.01)."""
     a = rng.matrix(0, 0, 16, 16, rng.UNIFORM, 1.0, np.float16)
     b = rng.matrix(0, 1, 16, 16, rng.UNIFORM, 1.0, np.float16)
