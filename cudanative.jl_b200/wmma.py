@@ -27,8 +27,6 @@ kernel (examples/wmma/high-level.jl:30-44) as one launch.
 """
 from __future__ import annotations
 
-import ctypes as C
-
 import numpy as np
 
 from . import _lib

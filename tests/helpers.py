@@ -4,7 +4,7 @@ from __future__ import annotations
 import numpy as np
 
 from cudanative_jl_b200 import _lib, rng
-from cudanative_jl_b200.array import Array, CuArray, CuHostArray
+from cudanative_jl_b200.array import Array, CuArray
 
 
 def operands(M, N, K, transA, transB, seed, *, a_scale=None, c_dist=rng.UNIFORM, lda=None, ldb=None):

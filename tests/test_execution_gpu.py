@@ -5,7 +5,7 @@ import ctypes as C
 import numpy as np
 import pytest
 
-from cudanative_jl_b200 import B200Error, _lib, wmma
+from cudanative_jl_b200 import _lib, wmma
 from cudanative_jl_b200.array import Array, CuArray, pointer, similar
 from cudanative_jl_b200.execution import blockIdx, cuda, synchronize, threadIdx
 

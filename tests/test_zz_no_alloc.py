@@ -8,8 +8,6 @@ and status word) is a 16 MiB array inside the library image, shared by every cal
 the test makes two calls in a row with different problems and checks that neither sees the other's
 leftovers.  Collected last on purpose (file name): if it fails under ``-x`` every other test has
 already run."""
-import ctypes as C
-
 import numpy as np
 import pytest
 
