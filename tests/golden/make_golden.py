@@ -46,6 +46,17 @@ def main():
     c = rng.matrix(2, 2, M, N, rng.UNIFORM, 1.0, np.float32)
     np.savez(HERE / "config3_small.npz", a=a, b=b, c=c, d=oracle.gemm_ref(True, False, 2.0, a, b, 0.5, c),
              d64=oracle.gemm_c(True, False, 2.0, a.astype(np.float32), b.astype(np.float32), 0.5, c, True))
+    # 4. bfloat16 operands (bit patterns in uint16), two matrices of a batch: 72 x 40 x 136, alpha=1.25, beta=0.5, seed 6;
+    #    outputs in binary32 and, rounded once more, in bfloat16
+    M, N, K = 72, 40, 136
+    fix = {}
+    for i in range(2):
+        a = oracle.bf16_round(rng.matrix(6 + i, 0, M, K, rng.NORMAL, K ** -0.5, np.float32))
+        b = oracle.bf16_round(rng.matrix(6 + i, 1, K, N, rng.NORMAL, 1.0, np.float32))
+        c = rng.matrix(6 + i, 2, M, N, rng.UNIFORM, 1.0, np.float32)
+        d = oracle.gemm_c(False, False, 1.25, oracle.bf16_widen(a), oracle.bf16_widen(b), 0.5, c, True)
+        fix.update({f"a{i}": a, f"b{i}": b, f"c{i}": c, f"d{i}": d, f"d{i}_bf16": oracle.bf16_round(d)})
+    np.savez(HERE / "bf16_batch_small.npz", **fix)
     print("wrote", sorted(p.name for p in HERE.glob("*.npz")))
 
 

@@ -95,6 +95,23 @@ def test_golden_config3_small(oracle):
     assert np.array_equal(d64, g["d64"])                            # the C loop is deterministic
 
 
+def test_golden_bf16_batch(oracle, pkg):
+    """bfloat16 operands: the stored results are the C loop with double accumulation on the widened inputs;
+    the sgemm statement agrees within the acceptance, both roundings to bfloat16 (oracle and library helper)
+    reproduce the stored bits."""
+    from cudanative_jl_b200.bfloat16 import round_to_bf16, widen_bf16
+    g = np.load(GOLDEN / "bf16_batch_small.npz")
+    for i in range(2):
+        a, b, c = g[f"a{i}"], g[f"b{i}"], g[f"c{i}"]
+        assert a.dtype == np.uint16 and np.array_equal(oracle.bf16_round(oracle.bf16_widen(a)), a)
+        d64 = oracle.gemm_c(False, False, 1.25, oracle.bf16_widen(a), oracle.bf16_widen(b), 0.5, c, True)
+        assert np.array_equal(d64, g[f"d{i}"])
+        oracle.assert_close(oracle.gemm_ref(False, False, 1.25, oracle.bf16_widen(a), oracle.bf16_widen(b), 0.5, c), g[f"d{i}"])
+        assert np.array_equal(oracle.bf16_round(g[f"d{i}"]), g[f"d{i}_bf16"])
+        assert np.array_equal(round_to_bf16(g[f"d{i}"]), g[f"d{i}_bf16"])
+        assert np.array_equal(widen_bf16(a), oracle.bf16_widen(a))
+
+
 def test_acceptance_thresholds_reject_wrong_answers(oracle):
     g = np.load(GOLDEN / "config3_small.npz")
     bad = g["d"].copy()
