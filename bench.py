@@ -8,7 +8,9 @@ Workloads (all synthetic, from the counter-based generator of the library):
     gemm4096  M=N=K=4096, A, B column-major, alpha=beta=1, seed 1
     skinny    M=16384, N=128, K=8192, A, B column-major, beta=0, seed 3              (HBM-bound)
     sharded   M=N=32768, K=16384, A, B column-major, alpha=beta=1, seed 4; B/C/D split into
-              column slabs over the ranks, A broadcast from rank 0 with NCCL        (default at N>1)
+              column slabs over the ranks; A travels from rank 0 to every rank in K panels over
+              NVLink: copy-engine scatter + all-gather through the b200_sharded_* entry points
+              (--transport p2p, default) or NCCL broadcast (--transport nccl)       (default at N>1)
 Secondary workloads (1 GPU, device-resident timing only; no e2e / CPU leg):
     gemm8192_bf16  gemm8192 with bfloat16 A and B (b200_gemm_ex)
     batched64      64 products of 1024^3, Float16 in, Float32 C and D, alpha=beta=1, one launch
@@ -19,6 +21,12 @@ timed with CUDA events on the launching stream (max over ranks); `e2e` is the sa
 the host-buffer entry point, host<->device copies inside the timed region.  `--impl reference`
 times the CPU statement of the same product (float32 sgemm on the Float16-rounded inputs -- the
 stand-in for Julia's LinearAlgebra.mul!, which cannot run without Julia) on the host cores.
+
+The default one-GPU line also carries, as extra keys, the other single-GPU configurations and the
+denominator of the multi-GPU values: `sustained` (the 8192^3 product back to back for >= 2 s),
+`skinny`, `gemm4096` and `scaling_baseline` (the sharded workload on one GPU).  Sharded runs check
+sampled tiles of every rank's D slab against the CPU oracle after the timed region (`parity`) and
+exit non-zero when they differ.
 """
 from __future__ import annotations
 
@@ -77,21 +85,68 @@ def algorithmic_bytes(w):
 # clocks
 # ---------------------------------------------------------------------------------------------
 class ClockSampler:
-    """nvidia-smi samples of SM clock and throttle reasons while the timed region runs."""
+    """SM clock and throttle reasons while a timed region runs.  Reads NVML directly when the Python
+    binding is there (a sample every ~2 ms, so that a region of a few milliseconds still gets
+    several), else parses `nvidia-smi -lms`.  Only reads: no clock, power or mode setting is touched."""
 
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
              "clocks_event_reasons.sw_power_cap")
+    # NVML clocks-event-reason bits
+    NVML_REASONS = ((0x4, "sw_power_cap"), (0x8, "hw_slowdown"), (0x20, "sw_thermal_slowdown"), (0x40, "hw_thermal_slowdown"))
 
-    def __init__(self, gpu_index: int):
+    def __init__(self, gpu_index: int, uuid: str | None = None):
         self.gpu_index = gpu_index
+        self.uuid = uuid
         self.proc = None
-        self.lines = []
+        self.lines = []      # (t, nvidia-smi csv line)
+        self.samples = []    # (t, sm_mhz, reasons bitmask) from NVML
+        self.smax = None
+        self._stop = False
+        self._thread = None
+
+    def _nvml_handle(self):
+        import pynvml
+
+        pynvml.nvmlInit()
+        if self.uuid:
+            for cand in (self.uuid, "GPU-" + self.uuid):
+                try:
+                    return pynvml, pynvml.nvmlDeviceGetHandleByUUID(cand.encode() if isinstance(cand, str) else cand)
+                except Exception:
+                    try:
+                        return pynvml, pynvml.nvmlDeviceGetHandleByUUID(cand)
+                    except Exception:
+                        continue
+        return pynvml, pynvml.nvmlDeviceGetHandleByIndex(self.gpu_index)
 
     def start(self):
         try:
+            nv, dev = self._nvml_handle()
+            self.smax = float(nv.nvmlDeviceGetMaxClockInfo(dev, nv.NVML_CLOCK_SM))
+            nv.nvmlDeviceGetClockInfo(dev, nv.NVML_CLOCK_SM)
+
+            def pump():
+                while not self._stop:
+                    try:
+                        mhz = float(nv.nvmlDeviceGetClockInfo(dev, nv.NVML_CLOCK_SM))
+                        try:
+                            why = int(nv.nvmlDeviceGetCurrentClocksEventReasons(dev))
+                        except Exception:
+                            why = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(dev))
+                        self.samples.append((time.perf_counter(), mhz, why))
+                    except Exception:
+                        pass
+                    time.sleep(0.002)
+
+            self._thread = threading.Thread(target=pump, daemon=True)
+            self._thread.start()
+            return
+        except Exception:
+            self._thread = None
+        try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.QUERY}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._pump, daemon=True).start()
         except Exception:
@@ -101,17 +156,15 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append((time.perf_counter(), line.strip()))
 
-    def stop(self, t0: float, t1: float) -> dict:
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        time.sleep(0.15)
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except Exception:
-            self.proc.kill()
+    def window(self, t0: float, t1: float) -> dict:
+        """Median clock and the reasons seen between two perf_counter times (sampling goes on)."""
+        if self._thread is not None:
+            got = [(m, w) for (t, m, w) in list(self.samples) if t0 <= t <= t1]
+            reasons = sorted({name for (_, w) in got for (bit, name) in self.NVML_REASONS if w & bit})
+            return {"sm_mhz": float(np.median([m for (m, _) in got])) if got else None, "sm_max_mhz": self.smax,
+                    "reasons": reasons, "samples": len(got)}
         sm, smax, reasons = [], None, set()
-        for (t, line) in self.lines:
+        for (t, line) in list(self.lines):
             if t < t0 - 0.05 or t > t1 + 0.15:
                 continue
             f = [x.strip() for x in line.split(",")]
@@ -128,10 +181,41 @@ class ClockSampler:
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": smax, "reasons": sorted(reasons),
                 "samples": len(sm)}
 
+    def stop(self, t0: float, t1: float) -> dict:
+        if self._thread is not None:
+            out = self.window(t0, t1)
+            self._stop = True
+            return out
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        return self.window(t0, t1)
+
 
 # ---------------------------------------------------------------------------------------------
 # CPU statement (oracle) legs
 # ---------------------------------------------------------------------------------------------
+def use_all_host_threads() -> int:
+    """torchrun exports OMP_NUM_THREADS=1 to its ranks, which would turn the BLAS behind numpy into a
+    one-thread library: raise the pool to every host core explicitly and report what it ended up with."""
+    want = os.cpu_count() or 1
+    try:
+        import threadpoolctl
+
+        threadpoolctl.threadpool_limits(limits=want)
+        got = [int(i.get("num_threads", 0)) for i in threadpoolctl.threadpool_info() if i.get("user_api") == "blas"]
+        if got:
+            return max(got)
+    except Exception:
+        pass
+    return int(os.environ.get("OMP_NUM_THREADS", want))
+
+
 class CpuSample:
     """float32 sgemm on a bounded slab of the workload: rows 0..m_s-1 of op(A), full K, the first
     n_cols columns of B and C.  Operands are generated once; ``run()`` times one product."""
@@ -141,7 +225,7 @@ class CpuSample:
         rng = entry.load_package().rng
         self.w = w
         M, K, N = w["M"], w["K"], w["N"]
-        self.cores = os.cpu_count() or 1
+        self.cores = use_all_host_threads()
         m_s = min(M, 8192)
         a16 = rng.window(w["seed"], 0, (K if w["transA"] else M), 0, (K if w["transA"] else m_s), 0,
                          (m_s if w["transA"] else K), rng.NORMAL, K ** -0.5, np.float16)
@@ -159,7 +243,7 @@ class CpuSample:
         self.b32 = rng.window(w["seed"], 1, K, 0, K, 0, n_cols, rng.NORMAL, b_scale, np.float16).astype(np.float32)
         self.c = np.zeros((m_s, n_cols), np.float32, order="F")
         self.flops = 2.0 * m_s * n_cols * K
-        self.desc = (f"float32 sgemm (numpy/OpenBLAS) on Float16-rounded inputs, rows 0..{m_s - 1} x cols 0..{n_cols - 1} "
+        self.desc = (f"float32 sgemm (numpy/OpenBLAS, {self.cores} threads) on Float16-rounded inputs, rows 0..{m_s - 1} x cols 0..{n_cols - 1} "
                      f"x full K={K} of the workload")
 
     def _gemm(self, b32, c):
@@ -189,10 +273,79 @@ def cpu_sample(w, target_seconds=12.0):
 
 
 # ---------------------------------------------------------------------------------------------
+# parity of a sharded product (checker leg: the CPU oracle on sampled tiles)
+# ---------------------------------------------------------------------------------------------
+def check_slab_tiles(w, D, n0, ns, A=None, tiles=8, tile=128, seed=1234):
+    """Compare sampled tile x tile blocks of a column slab of D (device tensor, column-major M x ns,
+    columns [n0, n0+ns) of the workload) with the CPU oracle: `tiles` blocks at random places plus one
+    on the slab's first and one on its last columns, each with the full K.  The operands of a block
+    are regenerated from the counter-based generator, so no other rank is needed.  When `A` (device
+    tensor, M x K column-major) is given, sampled columns of it are compared bit for bit with the
+    generator as well (did A arrive intact on this rank?).  Returns a dict; never raises."""
+    oracle = entry.load_oracle()
+    rng = entry.load_package().rng
+    M, K = w["M"], w["K"]
+    out = {"tiles": 0, "rel_fro_max": 0.0, "elem_max": 0.0, "a_columns": 0, "ok": True, "why": None}
+    if ns <= 0:
+        return out
+    rs = np.random.RandomState(seed + n0)
+    tm, tn = min(tile, M), min(tile, ns)
+    places = [(int(rs.randint(0, M - tm + 1)), 0), (int(rs.randint(0, M - tm + 1)), ns - tn)]
+    places += [(int(rs.randint(0, M - tm + 1)), int(rs.randint(0, ns - tn + 1))) for _ in range(tiles)]
+    b_scale = K ** -0.5 if w["b_rsqrt"] else 1.0
+    d2 = D.view(ns, M)  # torch sees the column-major slab as its transpose
+    for (r0, c0) in places:
+        a = rng.window(w["seed"], 0, M, r0, r0 + tm, 0, K, rng.NORMAL, K ** -0.5, np.float16)
+        b = rng.window(w["seed"], 1, K, 0, K, n0 + c0, n0 + c0 + tn, rng.NORMAL, b_scale, np.float16)
+        c = None
+        if w["beta"] != 0.0:
+            c = rng.window(w["seed"], 2, M, r0, r0 + tm, n0 + c0, n0 + c0 + tn, dist_code(rng, w["c_dist"]), 1.0, np.float32)
+        ref = oracle.gemm_ref(False, False, w["alpha"], a, b, w["beta"], c)
+        got = d2[c0:c0 + tn, r0:r0 + tm].cpu().numpy().T
+        out["tiles"] += 1
+        if not np.all(np.isfinite(got)):
+            out["ok"], out["why"] = False, f"non-finite values in rows {r0}.. cols {n0 + c0}.."
+            continue
+        rel, elem = oracle.errors(got, ref)
+        out["rel_fro_max"] = max(out["rel_fro_max"], rel)
+        out["elem_max"] = max(out["elem_max"], elem)
+        if rel > oracle.REL_FRO_TOL or elem > oracle.ELEM_TOL:
+            out["ok"], out["why"] = False, f"tile rows {r0}.. cols {n0 + c0}..: rel {rel:.3e}, elem {elem:.3e}"
+    if A is not None:
+        a2 = A.view(K, M)
+        cols = sorted({0, K - 1, *[int(x) for x in rs.randint(0, K, size=14)]})
+        for k in cols:
+            want = rng.window(w["seed"], 0, M, 0, M, k, k + 1, rng.NORMAL, K ** -0.5, np.float16)[:, 0]
+            got = a2[k].cpu().numpy()
+            out["a_columns"] += 1
+            if not np.array_equal(got.view(np.uint16), want.view(np.uint16)):
+                out["ok"], out["why"] = False, f"column {k} of A differs from what rank 0 holds"
+    out["rel_fro_max"] = float(f"{out['rel_fro_max']:.3e}")
+    out["elem_max"] = float(f"{out['elem_max']:.3e}")
+    return out
+
+
+# ---------------------------------------------------------------------------------------------
 # GPU legs
 # ---------------------------------------------------------------------------------------------
 def dist_code(rng, name):
     return {"uniform": rng.UNIFORM, "normal": rng.NORMAL, "zeros": rng.ZEROS}[name]
+
+
+def event_timed(torch, fn, steps, warmup):
+    """(total ms, perf_counter window) of `steps` calls of fn after `warmup` untimed ones, CUDA events
+    on the current stream."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    ev0.record()
+    for _ in range(steps):
+        fn()
+    ev1.record()
+    torch.cuda.synchronize()
+    return ev0.elapsed_time(ev1), (t0, time.perf_counter())
 
 
 def run_ours(args):
@@ -200,7 +353,8 @@ def run_ours(args):
 
     pkg = entry.load_package()
     from cudanative_jl_b200 import _lib, rng
-    from cudanative_jl_b200.gemm import Handle, ShardedGemm, init_nccl_env
+    from cudanative_jl_b200.gemm import Handle, ShardedGemm
+    from cudanative_jl_b200.nccl_broadcast import NcclBroadcastGemm, init_nccl_env
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -227,15 +381,36 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    def max_over_ranks(x):
+        if dist is None:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
     sharded = name == "sharded"
-    if sharded:
-        sg = ShardedGemm(h, M, N, K, panels=args.panels, transport=args.transport, fused=args.gated,
-                         reserve_ctas=args.nccl_ctas if args.transport == "nccl" else 0)
+    p2p = sharded and (args.transport == "p2p" or world == 1)
+    sg = None
+    if sharded and p2p:
+        def exchange(blob):
+            blobs = [None] * world
+            dist.all_gather_object(blobs, blob)
+            return blobs
+        sg = ShardedGemm(h, M, N, K, rank=rank, world=world, panels=args.panels, exchange=exchange if world > 1 else None)
         n0, ns = sg.n0, sg.slab_cols
+        A = torch.as_tensor(sg.a_view(), device=torch.device("cuda", local_rank))
+        n_launches = 1 if args.gated else sg.n_groups
+        n_panels = sg.n_panels
+    elif sharded:
+        sg = NcclBroadcastGemm(h, M, N, K, panels=args.panels, reserve_ctas=args.nccl_ctas)
+        n0, ns = sg.n0, sg.slab_cols
+        A = torch.empty(M * K, dtype=torch.float16, device="cuda")
+        n_launches = n_panels = len(sg.panels)
     else:
-        sg, n0, ns = None, 0, N
+        n0, ns = 0, N
     a_rows, a_cols = (K, M) if w["transA"] else (M, K)
-    A = sg.alloc_a() if sharded else torch.empty(a_rows * a_cols, dtype=torch.float16, device="cuda")
+    if not sharded:
+        A = torch.empty(a_rows * a_cols, dtype=torch.float16, device="cuda")
     B = torch.empty(K * max(ns, 1), dtype=torch.float16, device="cuda")
     Cm = torch.empty(M * max(ns, 1), dtype=torch.float32, device="cuda") if w["beta"] != 0.0 else None
     D = torch.empty(M * max(ns, 1), dtype=torch.float32, device="cuda")
@@ -247,8 +422,10 @@ def run_ours(args):
     if Cm is not None:
         rng.fill_device(Cm.data_ptr(), M, ns, M, w["seed"], 2, dist_code(rng, w["c_dist"]), 1.0, False, stream, col0=n0)
 
-    def step():
-        if sharded:
+    def step(no_transfer=False):
+        if sharded and p2p:
+            sg.run(w["alpha"], B, w["beta"], Cm, D, stream=stream, gated=args.gated, no_transfer=no_transfer)
+        elif sharded:
             sg.run(w["alpha"], A, B, w["beta"], Cm, D)
         else:
             h.gemm(w["transA"], w["transB"], M, N, K, w["alpha"], A.data_ptr(), a_rows, B.data_ptr(), K, w["beta"],
@@ -262,8 +439,14 @@ def run_ours(args):
         raise SystemExit(f"device wait {code} ran out in block {block} during warm-up")
     launch = h.last_launch()
 
-    sampler = ClockSampler(local_rank) if rank == 0 else None
-    if sampler:
+    sampler = None
+    if rank == 0:
+        uuid = None
+        try:
+            uuid = str(torch.cuda.get_device_properties(local_rank).uuid)
+        except Exception:
+            pass
+        sampler = ClockSampler(local_rank, uuid)
         sampler.start()
         time.sleep(0.25)
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -275,18 +458,41 @@ def run_ours(args):
     ev1.record()
     barrier()
     t_wall1 = time.perf_counter()
-    ms_total = ev0.elapsed_time(ev1)
-    if dist is not None:
-        t = torch.tensor([ms_total], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total = float(t.item())
-    clocks = sampler.stop(t_wall0, t_wall1) if sampler else None
+    ms_total = max_over_ranks(ev0.elapsed_time(ev1))
+    clocks = sampler.window(t_wall0, t_wall1) if sampler else None
     code, block, _ = h.device_status()
     if code:
         raise SystemExit(f"device wait {code} ran out in block {block} during the timed region")
     ms_step = ms_total / args.steps
     flops = 2.0 * M * N * K
     tflops = flops / (ms_step * 1e-3) / 1e12
+
+    # ---- sharded runs: the result proves itself, and the exposed transfer becomes a number -------------
+    parity = None
+    compute_only_ms = None
+    if sharded:
+        mine = check_slab_tiles(w, D, n0, ns, A=A if rank != 0 else None)
+        if dist is not None:
+            t = torch.tensor([mine["tiles"], mine["a_columns"], 0.0 if mine["ok"] else 1.0], dtype=torch.float64, device="cuda")
+            dist.all_reduce(t)
+            m = torch.tensor([mine["rel_fro_max"], mine["elem_max"]], dtype=torch.float64, device="cuda")
+            dist.all_reduce(m, op=dist.ReduceOp.MAX)
+            whys = [None] * world
+            dist.all_gather_object(whys, mine["why"])
+            parity = {"tiles": int(t[0].item()), "a_columns": int(t[1].item()), "rel_fro_max": float(m[0].item()),
+                      "elem_max": float(m[1].item()), "ok": t[2].item() == 0.0, "ranks": world,
+                      "why": next((f"rank {r}: {x}" for r, x in enumerate(whys) if x), None)}
+        else:
+            parity = dict(mine, ranks=1)
+        parity["tolerance"] = {"rel_fro": 1e-3, "elem": 1e-2}
+        if p2p and world > 1 and not args.gated:
+            # the same launches with A already resident on every rank: what is left of ms_per_step is the
+            # part of the transfer that the schedule does not hide
+            k = max(3, min(args.steps, 10))
+            barrier()
+            ms, _ = event_timed(torch, lambda: step(no_transfer=True), k, 2)
+            compute_only_ms = max_over_ranks(ms / k)
+            barrier()
 
     # ---- end to end through the host-buffer API -------------------------------------------
     e2e_steps = max(1, min(args.steps, args.e2e_steps))
@@ -306,7 +512,7 @@ def run_ours(args):
                 A.copy_(hA, non_blocking=True)
             B.copy_(hB, non_blocking=True)
             Cm.copy_(hC, non_blocking=True)
-            sg.run(w["alpha"], A, B, w["beta"], Cm, D)
+            step()
             hD.copy_(D, non_blocking=True)
             torch.cuda.current_stream().synchronize()
         h2d = (hA.numel() * 2 if hA is not None else 0) + hB.numel() * 2 + hC.numel() * 4
@@ -343,13 +549,9 @@ def run_ours(args):
     for _ in range(e2e_steps):
         e2e_step()
     barrier()
-    e2e_s = (time.perf_counter() - t0) / e2e_steps
-    if dist is not None:
-        t = torch.tensor([e2e_s], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_s = float(t.item())
+    e2e_s = max_over_ranks((time.perf_counter() - t0) / e2e_steps)
     e2e_tflops = flops / e2e_s / 1e12
-    if sharded:
+    if sharded and p2p:
         barrier()
         sg.close()
 
@@ -357,7 +559,7 @@ def run_ours(args):
         if dist is not None:
             dist.destroy_process_group()
         return
-    launches_per_step = ((1 if sg.fused else len(sg.groups)) if sharded else 1) * (2 if launch["split_k"] > 1 else 1)
+    launches_per_step = (n_launches if sharded else 1) * (2 if launch["split_k"] > 1 else 1)
     hbm_bound = name == "skinny"
     # kernel-level roofline: one launch == one step for the single-GPU workloads
     if hbm_bound:
@@ -370,7 +572,13 @@ def run_ours(args):
         peak = peaks["tf_sustained"] if long_run else peaks["tf_burst"]
         peak_kind = "bf16_tflops_sustained" if long_run else "bf16_tflops"
         unit = "TFLOP/s"
-    traffic = load_traffic(name)
+    if sharded:
+        how = (f"N-sharded x{world}, A sent in {n_panels} K-panels by " +
+               ("NCCL broadcast, one GEMM launch per panel" if not p2p else
+                "copy-engine scatter + all-gather over NVLink ordered by stream memory operations (b200_sharded_run)" +
+                (", one gated GEMM launch" if args.gated else f", {n_launches} GEMM launches over growing K ranges")))
+    else:
+        how = "1 GPU"
     out = {
         "metric": METRIC, "value": round(tflops, 2), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": round(ms_step, 5), "higher_is_better": True,
@@ -378,19 +586,40 @@ def run_ours(args):
         "config": {"workload": name, "M": M, "N": N, "K": K, "transA": w["transA"], "transB": w["transB"],
                    "alpha": w["alpha"], "beta": w["beta"], "seed": w["seed"],
                    "l2": f"inputs+outputs {algorithmic_bytes(w) / 1e6:.0f} MB per step exceed the 126 MB L2; no flush",
-                   "kernel": launch, "parallelism": (f"N-sharded x{world}, A sent in {len(sg.panels)} K-panels by " + ("NCCL broadcast" if sg.transport == "nccl" else "copy-engine scatter + all-gather over NVLink ordered by stream memory operations" + (", one gated GEMM launch" if sg.fused else f", {len(sg.groups)} GEMM launches over growing K ranges"))) if sharded else "1 GPU"},
+                   "kernel": launch, "parallelism": how},
         "clocks": clocks,
         "e2e": {"value": round(e2e_tflops, 3), "unit": "TFLOP/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
-                "steps": e2e_steps, "api": "ShardedGemm.run + pinned copies" if sharded else "b200_gemm_f16f32_host"},
+                "steps": e2e_steps, "api": "b200_sharded_run + pinned copies" if sharded else "b200_gemm_f16f32_host"},
         "gpu_launches": launches_per_step * args.steps * world,
+        # traffic: DRAM bytes per launch come from an ncu capture; none has been taken of this build's kernel
+        # inside this run, so the line does not claim one (the summaries under profiles/ say which build they saw)
         "roofline": {"bound": "hbm" if hbm_bound else "tensor", "achieved": round(achieved, 2), "peak": peak, "unit": unit,
-                     "frac": round(achieved / peak, 4), "traffic": traffic, "peak_source": f"{peaks['source']} ({peak_kind})",
-                     "nominal_frac": round(achieved / (8000.0 if hbm_bound else 2250.0), 4)},
+                     "frac": round(achieved / peak, 4), "traffic": None, "peak_source": f"{peaks['source']} ({peak_kind})",
+                     "nominal_frac": round(achieved / (8000.0 if hbm_bound else 2250.0), 4),
+                     "algorithmic_bytes": algorithmic_bytes(w)},
     }
-    if world == 1 and args.workload is None and not args.no_scaling_baseline:
-        # The multi-GPU lines (N > 1) time the sharded 32768 x 32768 x 16384 product; its one-GPU time is measured
-        # here so that the N-GPU values have a like-for-like denominator next to the headline 8192^3 number.
-        out["scaling_baseline"] = sharded_on_one_gpu(h, stream)
+    if clocks and clocks.get("sm_mhz"):
+        out["clocks"]["ms_x_mhz"] = round(ms_step * clocks["sm_mhz"], 1)
+    if parity is not None:
+        out["parity"] = parity
+    if compute_only_ms is not None:
+        out["compute_only_ms"] = round(compute_only_ms, 4)
+        out["exposed_transfer_ms"] = round(ms_step - compute_only_ms, 4)
+    if world == 1 and args.workload is None:
+        # the other single-GPU configurations, each timed on its own: they share the line so that one
+        # default run records every headline figure
+        del A, B, Cm, D
+        torch.cuda.empty_cache()
+        if not args.no_extras:
+            out["sustained"] = sustained_loop(h, stream, peaks, sampler)
+            out["skinny"] = skinny_leg(h, stream, peaks, sampler)
+            out["gemm4096"] = square_leg(h, stream, "gemm4096", peaks, sampler)
+        if not args.no_scaling_baseline:
+            # The multi-GPU lines (N > 1) time the sharded 32768 x 32768 x 16384 product; its one-GPU time is measured
+            # here so that the N-GPU values have a like-for-like denominator next to the headline 8192^3 number.
+            out["scaling_baseline"] = sharded_on_one_gpu(h, stream, sampler)
+    if sampler:
+        sampler.stop(0, 0)
     if world == 1 and not args.no_cpu:
         v, cores, desc, secs = cpu_sample(w)
         out["cpu_baseline"] = {"value": round(v, 4), "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": desc,
@@ -398,6 +627,145 @@ def run_ours(args):
     print(json.dumps(out), flush=True)
     if dist is not None:
         dist.destroy_process_group()
+    if parity is not None and not parity["ok"]:
+        raise SystemExit(f"parity check failed: {parity['why']}")
+    sb = out.get("scaling_baseline")
+    if sb and not sb["parity"]["ok"]:
+        raise SystemExit(f"parity check of the one-GPU sharded run failed: {sb['parity']['why']}")
+
+
+def _operands(torch, rng, w, stream, a_copies=1):
+    """Device operands of a workload (column-major, filled from the generator); `a_copies` independent
+    buffers of A so that an HBM-bound kernel never finds its stream in L2."""
+    M, N, K = w["M"], w["N"], w["K"]
+    a_rows, a_cols = (K, M) if w["transA"] else (M, K)
+    As = []
+    for i in range(a_copies):
+        A = torch.empty(a_rows * a_cols, dtype=torch.float16, device="cuda")
+        rng.fill_device(A.data_ptr(), a_rows, a_cols, a_rows, w["seed"] + 1000 * i, 0, rng.NORMAL, K ** -0.5, True, stream)
+        As.append(A)
+    B = torch.empty(K * N, dtype=torch.float16, device="cuda")
+    rng.fill_device(B.data_ptr(), K, N, K, w["seed"], 1, rng.NORMAL, K ** -0.5 if w["b_rsqrt"] else 1.0, True, stream)
+    Cm = None
+    if w["beta"] != 0.0:
+        Cm = torch.empty(M * N, dtype=torch.float32, device="cuda")
+        rng.fill_device(Cm.data_ptr(), M, N, M, w["seed"], 2, dist_code(rng, w["c_dist"]), 1.0, False, stream)
+    D = torch.empty(M * N, dtype=torch.float32, device="cuda")
+    return As, B, Cm, D, a_rows
+
+
+def _status_or_exit(h, what):
+    code, block, _ = h.device_status()
+    if code:
+        raise SystemExit(f"device wait {code} ran out in block {block} in {what}")
+
+
+def sustained_loop(h, stream, peaks, sampler, seconds=2.2):
+    """The headline product back to back for at least two seconds: what the power cap leaves of the
+    burst figure.  Compared with the measured sustained cuBLAS rate."""
+    import torch
+    from cudanative_jl_b200 import rng
+
+    w = WORKLOADS["gemm8192"]
+    M, N, K = w["M"], w["N"], w["K"]
+    (A,), B, Cm, D, a_rows = _operands(torch, rng, w, stream)
+
+    def step():
+        h.gemm(w["transA"], w["transB"], M, N, K, w["alpha"], A.data_ptr(), a_rows, B.data_ptr(), K, w["beta"], Cm.data_ptr(), M,
+               D.data_ptr(), M, stream=stream)
+    ms, _ = event_timed(torch, step, 50, 3)
+    launches = max(200, int(seconds * 1e3 / (ms / 50)))
+    ms, (t0, t1) = event_timed(torch, step, launches, 0)
+    _status_or_exit(h, "the sustained loop")
+    tf = 2.0 * M * N * K / (ms / launches * 1e-3) / 1e12
+    clocks = sampler.window(t0 + 0.2, t1) if sampler else None
+    out = {"workload": "gemm8192", "launches": launches, "seconds": round(ms * 1e-3, 3), "ms_per_step": round(ms / launches, 5),
+           "value": round(tf, 2), "unit": "TFLOP/s", "peak": peaks["tf_sustained"], "frac": round(tf / peaks["tf_sustained"], 4),
+           "peak_source": f"{peaks['source']} (bf16_tflops_sustained)", "nominal_frac": round(tf / 2250.0, 4), "clocks": clocks}
+    if clocks and clocks.get("sm_mhz"):
+        out["clocks"]["ms_x_mhz"] = round(ms / launches * clocks["sm_mhz"], 1)
+    return out
+
+
+def skinny_leg(h, stream, peaks, sampler, launches=400):
+    """Configuration 4 (HBM-bound): launches rotate over four independent copies of A (268 MB each, more
+    than the L2), so every launch streams its A from HBM."""
+    import torch
+    from cudanative_jl_b200 import rng
+
+    w = WORKLOADS["skinny"]
+    M, N, K = w["M"], w["N"], w["K"]
+    As, B, Cm, D, a_rows = _operands(torch, rng, w, stream, a_copies=4)
+    i = [0]
+
+    def step():
+        A = As[i[0] & 3]
+        i[0] += 1
+        h.gemm(False, False, M, N, K, w["alpha"], A.data_ptr(), a_rows, B.data_ptr(), K, 0.0, None, M, D.data_ptr(), M, stream=stream)
+    ms, (t0, t1) = event_timed(torch, step, launches, 8)
+    _status_or_exit(h, "the skinny leg")
+    us = ms / launches * 1e3
+    gbs = algorithmic_bytes(w) / (us * 1e-6) / 1e9
+    clocks = sampler.window(t0, t1) if sampler else None
+    return {"workload": "skinny", "M": M, "N": N, "K": K, "launches": launches, "a_buffers": 4, "us_per_launch": round(us, 3),
+            "achieved": round(gbs, 1), "unit": "GB/s", "algorithmic_bytes": algorithmic_bytes(w), "peak": peaks["hbm_gbs"],
+            "frac": round(gbs / peaks["hbm_gbs"], 4), "peak_source": f"{peaks['source']} (hbm_gbs)",
+            "nominal_frac": round(gbs / 8000.0, 4), "value": round(2.0 * M * N * K / (us * 1e-6) / 1e12, 2), "kernel": h.last_launch(),
+            "clocks": clocks}
+
+
+def square_leg(h, stream, name, peaks, sampler, launches=400):
+    """A tensor-bound single-GPU configuration, device-resident timing."""
+    import torch
+    from cudanative_jl_b200 import rng
+
+    w = WORKLOADS[name]
+    M, N, K = w["M"], w["N"], w["K"]
+    (A,), B, Cm, D, a_rows = _operands(torch, rng, w, stream)
+
+    def step():
+        h.gemm(w["transA"], w["transB"], M, N, K, w["alpha"], A.data_ptr(), a_rows, B.data_ptr(), K, w["beta"],
+               Cm.data_ptr() if Cm is not None else None, M, D.data_ptr(), M, stream=stream)
+    ms, (t0, t1) = event_timed(torch, step, launches, 5)
+    _status_or_exit(h, name)
+    tf = 2.0 * M * N * K / (ms / launches * 1e-3) / 1e12
+    return {"workload": name, "M": M, "N": N, "K": K, "launches": launches, "ms_per_step": round(ms / launches, 5),
+            "value": round(tf, 2), "unit": "TFLOP/s", "peak": peaks["tf_burst"], "frac": round(tf / peaks["tf_burst"], 4),
+            "peak_source": f"{peaks['source']} (bf16_tflops)", "nominal_frac": round(tf / 2250.0, 4), "kernel": h.last_launch(),
+            "clocks": sampler.window(t0, t1) if sampler else None}
+
+
+def sharded_on_one_gpu(h, stream, sampler=None, steps=10, warmup=3):
+    """The sharded workload (config 5) on a single GPU: the denominator of the multi-GPU speed-up.
+    Runs through the same entry point as the multi-GPU lines (b200_sharded_run with one rank) and
+    checks sampled tiles of D against the CPU oracle."""
+    import torch
+    from cudanative_jl_b200 import rng
+    from cudanative_jl_b200.gemm import ShardedGemm
+
+    w = WORKLOADS["sharded"]
+    M, N, K = w["M"], w["N"], w["K"]
+    sg = ShardedGemm(h, M, N, K, rank=0, world=1)
+    A = torch.as_tensor(sg.a_view(), device="cuda")
+    B = torch.empty(K * N, dtype=torch.float16, device="cuda")
+    Cm = torch.empty(M * N, dtype=torch.float32, device="cuda")
+    D = torch.empty(M * N, dtype=torch.float32, device="cuda")
+    rng.fill_device(A.data_ptr(), M, K, M, w["seed"], 0, rng.NORMAL, K ** -0.5, True, stream)
+    rng.fill_device(B.data_ptr(), K, N, K, w["seed"], 1, rng.NORMAL, K ** -0.5, True, stream)
+    rng.fill_device(Cm.data_ptr(), M, N, M, w["seed"], 2, rng.NORMAL, 1.0, False, stream)
+
+    def step():
+        sg.run(w["alpha"], B, w["beta"], Cm, D, stream=stream)
+    ms, (t0, t1) = event_timed(torch, step, steps, warmup)
+    ms /= steps
+    _status_or_exit(h, "the one-GPU sharded run")
+    parity = dict(check_slab_tiles(w, D, 0, N), ranks=1)
+    del A
+    sg.close()
+    del B, Cm, D
+    return {"workload": "sharded", "M": M, "N": N, "K": K, "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": round(ms, 4),
+            "value": round(2.0 * M * N * K / (ms * 1e-3) / 1e12, 2), "unit": "TFLOP/s", "parity": parity,
+            "clocks": sampler.window(t0, t1) if sampler else None}
 
 
 def run_extra(args):
@@ -489,51 +857,6 @@ def run_extra(args):
     print(json.dumps(out), flush=True)
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures summarised in
-# profiles/gemm8192_tcgen05_pair_256x256.md and profiles/skinny_tcgen05_128x128.md
-NCU_TRAFFIC = {"gemm8192": 1465122000 + 253011200, "skinny": 270598912 + 4099840}
-
-
-def sharded_on_one_gpu(h, stream, steps=4, warmup=2):
-    """The sharded workload (config 5) on a single GPU: the denominator of the multi-GPU speed-up."""
-    import torch
-    from cudanative_jl_b200 import rng
-
-    w = WORKLOADS["sharded"]
-    M, N, K = w["M"], w["N"], w["K"]
-    A = torch.empty(M * K, dtype=torch.float16, device="cuda")
-    B = torch.empty(K * N, dtype=torch.float16, device="cuda")
-    Cm = torch.empty(M * N, dtype=torch.float32, device="cuda")
-    D = torch.empty(M * N, dtype=torch.float32, device="cuda")
-    rng.fill_device(A.data_ptr(), M, K, M, w["seed"], 0, rng.NORMAL, K ** -0.5, True, stream)
-    rng.fill_device(B.data_ptr(), K, N, K, w["seed"], 1, rng.NORMAL, K ** -0.5, True, stream)
-    rng.fill_device(Cm.data_ptr(), M, N, M, w["seed"], 2, rng.NORMAL, 1.0, False, stream)
-
-    def step():
-        h.gemm(False, False, M, N, K, w["alpha"], A.data_ptr(), M, B.data_ptr(), K, w["beta"], Cm.data_ptr(), M, D.data_ptr(), M,
-               stream=stream)
-    for _ in range(warmup):
-        step()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize()
-    ev0.record()
-    for _ in range(steps):
-        step()
-    ev1.record()
-    torch.cuda.synchronize()
-    ms = ev0.elapsed_time(ev1) / steps
-    code, block, _ = h.device_status()
-    if code:
-        raise SystemExit(f"device wait {code} ran out in block {block} in the one-GPU sharded run")
-    del A, B, Cm, D
-    return {"workload": "sharded", "M": M, "N": N, "K": K, "n_gpus": 1, "steps": steps, "ms_per_step": round(ms, 4),
-            "value": round(2.0 * M * N * K / (ms * 1e-3) / 1e12, 2), "unit": "TFLOP/s"}
-
-
-def load_traffic(name):
-    return NCU_TRAFFIC.get(name)
-
-
 def run_reference(args):
     """CPU arm: the same product, float32 sgemm on the host cores, bounded sample per step."""
     rank = int(os.environ.get("RANK", "0"))
@@ -582,6 +905,7 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-scaling-baseline", action="store_true", help="N=1: skip the one-GPU run of the sharded workload")
+    ap.add_argument("--no-extras", action="store_true", help="N=1: skip the sustained / skinny / gemm4096 legs")
     args = ap.parse_args()
     if args.workload in EXTRA_WORKLOADS:
         if args.impl == "reference":

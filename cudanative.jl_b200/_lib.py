@@ -11,14 +11,16 @@ from pathlib import Path
 
 LIB_PATH = Path(__file__).resolve().parent / "libb200wmma.so"
 
-OK, INVALID_ARG, UNSUPPORTED, CUDA_ERROR, DEVICE_TIMEOUT, NO_DEVICE = range(6)
+OK, INVALID_ARG, UNSUPPORTED, CUDA_ERROR, DEVICE_TIMEOUT, NO_DEVICE, PEER_TIMEOUT = range(7)
 COL_MAJOR, ROW_MAJOR = 0, 1
 F16, F32, BF16 = 0, 1, 2
 MATRIX_A, MATRIX_B, ACCUMULATOR = 0, 1, 2
 LOWER_WARP, LOWER_TCGEN05 = 0, 1
 KERNEL_AUTO, KERNEL_TCGEN05, KERNEL_SIMPLE = 0, 1, 2
 (OPT_FORCE_KERNEL, OPT_MAX_CTAS, OPT_WAIT_BUDGET_NS, OPT_TILE_N, OPT_SPLIT_K, OPT_CTA_PAIR,
- OPT_RASTER_GROUP) = range(7)
+ OPT_RASTER_GROUP, OPT_CHECK_ON_CALL) = range(8)
+SHARDED_GATED, SHARDED_NO_TRANSFER = 1, 2
+SHARDED_MAX_RANKS, SHARDED_MAX_PANELS, SHARDED_BLOB_BYTES = 64, 32, 128
 
 _i, _i64, _u64, _f, _p, _sz = C.c_int, C.c_int64, C.c_uint64, C.c_float, C.c_void_p, C.c_size_t
 _pp = C.POINTER(C.c_void_p)
@@ -59,8 +61,18 @@ SIGNATURES = {
     "b200_host_free": (_i, [_p]),
     "b200_memcpy_h2d": (_i, [_p, _p, _sz, _p]),
     "b200_memcpy_d2h": (_i, [_p, _p, _sz, _p]),
-    "b200_p2p_begin": (_i, [_i, _i, _pp, C.c_uint32, _p, _p, _p]),
-    "b200_p2p_exchange": (_i, [_i, _i, _i64, C.POINTER(_i64), _i, _i, _pp, _pp, C.c_uint32, _p, _p, _p, _p]),
+    "b200_static_warmup": (_i, []),
+    "b200_static_status": (_i, [_ip, _ip, _ip]),
+    "b200_static_selftest_bounded_wait": (_i, [_p, _i64]),
+    "b200_sharded_create": (_i, [_pp, _p, _i, _i, _i64, _i64, _i64, _i]),
+    "b200_sharded_destroy": (_i, [_p]),
+    "b200_sharded_info": (_i, [_p, C.POINTER(_i64), C.POINTER(_i64), _pp, _pp, _ip, _ip]),
+    "b200_sharded_ipc_blob": (_i, [_p, _p]),
+    "b200_sharded_attach": (_i, [_p, _p]),
+    "b200_sharded_attach_local": (_i, [_p, _pp, _pp]),
+    "b200_sharded_run": (_i, [_p, _p, _f, _p, _i64, _f, _p, _i64, _p, _i64, _i]),
+    "b200_sharded_wait": (_i, [_p, _i64]),
+    "b200_sharded_layout": (_i, [_i, _i64, _i64, _i, C.POINTER(_i64), C.POINTER(_i64), _ip, _ip, _ip, C.POINTER(_i64)]),
     "b200_ipc_get_handle": (_i, [_p, _p]),
     "b200_ipc_open_handle": (_i, [_p, _pp]),
     "b200_ipc_close_handle": (_i, [_p]),

@@ -19,7 +19,7 @@ INCLUDE = PKG_DIR.parent / "include"
 BUILD_DIR = PKG_DIR / "build"
 LIB_PATH = PKG_DIR / "libb200wmma.so"
 
-SOURCES = ["api.cu", "gemm_sm100.cu", "gemm_simple.cu", "wmma_unit.cu", "noalloc.cu"]
+SOURCES = ["api.cu", "gemm_sm100.cu", "gemm_simple.cu", "wmma_unit.cu", "noalloc.cu", "sharded.cu"]
 HEADERS = ["ptx_sm100.cuh", "gemm_sm100.cuh", "internal.h", "rng.cuh", "wmma_frag.cuh"]
 
 NVCC_FLAGS = [

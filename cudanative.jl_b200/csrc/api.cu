@@ -44,29 +44,7 @@ int cuda_fail(cudaError_t e, const char* what) {
 
 using namespace b200;
 
-struct b200_handle {
-    int device = 0;
-    int sm_count = 0;
-    int* status_word = nullptr;  // 4 ints on the device
-    // options
-    int force_kernel = B200_KERNEL_AUTO;
-    int max_ctas = 0;
-    unsigned long long wait_budget_ns = 2000000000ull;
-    int tile_n = 0;
-    int split_k = 0;
-    int cta_pair = 0;
-    int raster_group = 0;
-    // workspace of the host-buffer entry point and split-K scratch (grown on demand)
-    void* ws[4] = {nullptr, nullptr, nullptr, nullptr};
-    size_t ws_bytes[4] = {0, 0, 0, 0};
-    float* scratch = nullptr;
-    size_t scratch_bytes = 0;
-    cudaStream_t streams[3] = {nullptr, nullptr, nullptr};  // upload / multiply / download
-    std::vector<cudaEvent_t> events;
-    LaunchInfo last = {0, 0, 0, 0, 0};
-};
-
-namespace {
+namespace b200 {
 
 int ensure_buffer(void** p, size_t* have, size_t need) {
     if (need <= *have) return B200_OK;
@@ -135,7 +113,7 @@ int check_current_device(const b200_handle* h) {
     return B200_OK;
 }
 
-int run_gemm(b200_handle* h, cudaStream_t stream, const GemmProblem& g) {
+int gemm_dispatch(b200_handle* h, cudaStream_t stream, const GemmProblem& g) {
     int rc = validate(g);
     if (rc) return rc;
     if (g.M == 0 || g.N == 0 || g.batch == 0) return B200_OK;
@@ -156,7 +134,7 @@ int run_gemm(b200_handle* h, cudaStream_t stream, const GemmProblem& g) {
             if (g.C) strip.C = reinterpret_cast<const float*>(reinterpret_cast<const char*>(g.C) + skip * elem_bytes(g.c_type));
             strip.D = reinterpret_cast<float*>(reinterpret_cast<char*>(g.D) + skip * elem_bytes(g.d_type));
             if ((rc = gemm_simple_launch(strip, stream, nullptr))) return rc;
-            return run_gemm(h, stream, top);
+            return gemm_dispatch(h, stream, top);
         }
     }
     if (kernel == B200_KERNEL_AUTO && !eligible && g.batch > 1) {
@@ -176,7 +154,7 @@ int run_gemm(b200_handle* h, cudaStream_t stream, const GemmProblem& g) {
                 one.B = static_cast<const char*>(g.B) + 2 * i * g.stride_b;
                 if (g.C) one.C = reinterpret_cast<const float*>(reinterpret_cast<const char*>(g.C) + i * g.stride_c * elem_bytes(g.c_type));
                 one.D = reinterpret_cast<float*>(reinterpret_cast<char*>(g.D) + i * g.stride_d * elem_bytes(g.d_type));
-                if ((rc = run_gemm(h, stream, one))) return rc;
+                if ((rc = gemm_dispatch(h, stream, one))) return rc;
             }
             return B200_OK;
         }
@@ -199,12 +177,56 @@ int run_gemm(b200_handle* h, cudaStream_t stream, const GemmProblem& g) {
 }
 
 int read_status(b200_handle* h, int* word) {
-    B200_CUDA_TRY(cudaMemcpy(word, h->status_word, 4 * sizeof(int), cudaMemcpyDeviceToHost));
-    if (word[0] != 0) B200_CUDA_TRY(cudaMemset(h->status_word, 0, 4 * sizeof(int)));
+    if (!h->poll_stream) B200_CUDA_TRY(cudaStreamCreateWithFlags(&h->poll_stream, cudaStreamNonBlocking));
+    if (!h->host_word) B200_CUDA_TRY(cudaHostAlloc(reinterpret_cast<void**>(&h->host_word), 4 * sizeof(int), cudaHostAllocDefault));
+    B200_CUDA_TRY(cudaMemcpyAsync(h->host_word, h->status_word, 4 * sizeof(int), cudaMemcpyDeviceToHost, h->poll_stream));
+    B200_CUDA_TRY(cudaStreamSynchronize(h->poll_stream));
+    for (int i = 0; i < 4; ++i) word[i] = h->host_word[i];
+    if (word[0] != 0) {
+        B200_CUDA_TRY(cudaMemsetAsync(h->status_word, 0, 4 * sizeof(int), h->poll_stream));
+        B200_CUDA_TRY(cudaStreamSynchronize(h->poll_stream));
+    }
     return B200_OK;
 }
 
-}  // namespace
+// B200_OPT_CHECK_ON_CALL: what the reference does in prepare_cuda_call (src/init.jl:37 ->
+// src/exceptions.jl:76-89 of CUDAnative.jl) -- before new work is enqueued, look at the failure
+// flag of work that has already finished.  Only a launch that is known to be complete is looked
+// at (event query), so the call never waits for the GPU.
+int poll_previous_launch(b200_handle* h) {
+    if (!h->check_on_call || !h->last_pending) return B200_OK;
+    cudaError_t e = cudaEventQuery(h->last_done);
+    if (e == cudaErrorNotReady) return B200_OK;
+    if (e != cudaSuccess) return cuda_fail(e, "cudaEventQuery(previous launch)");
+    h->last_pending = false;
+    int word[4] = {0, 0, 0, 0};
+    int rc = read_status(h, word);
+    if (rc) return rc;
+    if (word[0] != 0)
+        return fail(B200_DEVICE_TIMEOUT, "a bounded wait ran out on the device in an earlier launch of this handle (wait id " +
+                                             std::to_string(word[0]) + ", block " + std::to_string(word[1]) +
+                                             "); its result is not valid.  This call enqueued nothing.");
+    return B200_OK;
+}
+
+int note_launch(b200_handle* h, cudaStream_t stream) {
+    if (!h->check_on_call) return B200_OK;
+    if (!h->last_done) B200_CUDA_TRY(cudaEventCreateWithFlags(&h->last_done, cudaEventDisableTiming));
+    B200_CUDA_TRY(cudaEventRecord(h->last_done, stream));
+    h->last_pending = true;
+    return B200_OK;
+}
+
+// What every GEMM entry point of the C ABI runs: optional poll of the previous launch, dispatch,
+// bookkeeping for the next poll.
+int gemm_entry(b200_handle* h, cudaStream_t stream, const GemmProblem& g) {
+    int rc = poll_previous_launch(h);
+    if (rc) return rc;
+    if ((rc = gemm_dispatch(h, stream, g))) return rc;
+    return note_launch(h, stream);
+}
+
+}  // namespace b200
 
 extern "C" {
 
@@ -218,6 +240,7 @@ const char* b200_status_string(int status) {
         case B200_CUDA_ERROR: return "B200_CUDA_ERROR";
         case B200_DEVICE_TIMEOUT: return "B200_DEVICE_TIMEOUT";
         case B200_NO_DEVICE: return "B200_NO_DEVICE";
+        case B200_PEER_TIMEOUT: return "B200_PEER_TIMEOUT";
         default: return "B200_UNKNOWN_STATUS";
     }
 }
@@ -279,6 +302,9 @@ int b200_destroy(b200_handle* h) {
     for (int i = 0; i < 3; ++i)
         if (h->streams[i]) cudaStreamDestroy(h->streams[i]);
     for (cudaEvent_t e : h->events) cudaEventDestroy(e);
+    if (h->last_done) cudaEventDestroy(h->last_done);
+    if (h->poll_stream) cudaStreamDestroy(h->poll_stream);
+    if (h->host_word) cudaFreeHost(h->host_word);
     delete h;
     return B200_OK;
 }
@@ -314,6 +340,10 @@ int b200_set_option(b200_handle* h, int option, int64_t value) {
             if (value < 0 || value > 4096) return fail(B200_INVALID_ARG, "raster group must be in [0, 4096]");
             h->raster_group = static_cast<int>(value);
             return B200_OK;
+        case B200_OPT_CHECK_ON_CALL:
+            if (value != 0 && value != 1) return fail(B200_INVALID_ARG, "check_on_call must be 0 or 1");
+            h->check_on_call = static_cast<int>(value);
+            return B200_OK;
         default:
             return fail(B200_INVALID_ARG, "unknown option");
     }
@@ -329,6 +359,7 @@ int b200_get_option(b200_handle* h, int option, int64_t* value) {
         case B200_OPT_SPLIT_K: *value = h->split_k; return B200_OK;
         case B200_OPT_CTA_PAIR: *value = h->cta_pair; return B200_OK;
         case B200_OPT_RASTER_GROUP: *value = h->raster_group; return B200_OK;
+        case B200_OPT_CHECK_ON_CALL: *value = h->check_on_call; return B200_OK;
         default: return fail(B200_INVALID_ARG, "unknown option");
     }
 }
@@ -368,7 +399,7 @@ int b200_gemm_f16f32(b200_handle* h, b200_stream stream, int transA, int transB,
                      int64_t ldc, float* D, int64_t ldd) {
     if (!h) return fail(B200_INVALID_ARG, "null handle");
     GemmProblem g{transA, transB, M, N, K, alpha, beta, A, lda, B, ldb, C, ldc, D, ldd};
-    return run_gemm(h, static_cast<cudaStream_t>(stream), g);
+    return gemm_entry(h, static_cast<cudaStream_t>(stream), g);
 }
 
 int b200_gemm_f16_typed(b200_handle* h, b200_stream stream, int transA, int transB, int64_t M, int64_t N, int64_t K,
@@ -381,7 +412,7 @@ int b200_gemm_f16_typed(b200_handle* h, b200_stream stream, int transA, int tran
                   static_cast<float*>(D), ldd};
     g.c_type = c_type;
     g.d_type = d_type;
-    return run_gemm(h, static_cast<cudaStream_t>(stream), g);
+    return gemm_entry(h, static_cast<cudaStream_t>(stream), g);
 }
 
 namespace {
@@ -408,7 +439,7 @@ int b200_gemm_strided_batched(b200_handle* h, b200_stream stream, int transA, in
     g.stride_b = stride_b;
     g.stride_c = stride_c;
     g.stride_d = stride_d;
-    return run_gemm(h, static_cast<cudaStream_t>(stream), g);
+    return gemm_entry(h, static_cast<cudaStream_t>(stream), g);
 }
 
 int b200_gemm_ex(b200_handle* h, b200_stream stream, int transA, int transB, int64_t M, int64_t N, int64_t K,
@@ -435,7 +466,7 @@ int b200_gemm_f16f32_gated(b200_handle* h, b200_stream stream, int transA, int t
     const int saved = h->force_kernel, saved_split = h->split_k;
     h->force_kernel = B200_KERNEL_TCGEN05;
     h->split_k = 1;
-    rc = run_gemm(h, static_cast<cudaStream_t>(stream), g);
+    rc = gemm_entry(h, static_cast<cudaStream_t>(stream), g);
     h->force_kernel = saved;
     h->split_k = saved_split;
     return rc;
@@ -473,145 +504,6 @@ int b200_stream_wait_u32(b200_stream stream, void* dptr, uint32_t value) {
     return B200_OK;
 }
 
-}  // extern "C"
-
-namespace {
-
-// flag block layout (32-bit words): done[64] | scattered[32] (+32 spare) | gathered[32][64]
-inline size_t word_done(int g) { return 4u * static_cast<size_t>(g); }
-inline size_t word_scat(int p) { return 4u * (64u + static_cast<size_t>(p)); }
-inline size_t word_gath(int p, int g) { return 4u * (128u + static_cast<size_t>(p) * 64u + static_cast<size_t>(g)); }
-
-using BatchFn = CUresult (*)(CUstream, unsigned int, CUstreamBatchMemOpParams*, unsigned int);
-
-BatchFn batch_fn() {
-    static BatchFn fn = nullptr;
-    if (!fn) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuStreamBatchMemOp", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<BatchFn>(p);
-    }
-    return fn;
-}
-
-// One driver call for a list of 32-bit waits (>=) or writes on a stream.
-struct MemOps {
-    std::vector<CUstreamBatchMemOpParams> ops;
-    void wait(void* base, size_t off, uint32_t value) {
-        CUstreamBatchMemOpParams o;
-        std::memset(&o, 0, sizeof(o));
-        o.waitValue.operation = CU_STREAM_MEM_OP_WAIT_VALUE_32;
-        o.waitValue.address = reinterpret_cast<CUdeviceptr>(static_cast<char*>(base) + off);
-        o.waitValue.value = value;
-        o.waitValue.flags = CU_STREAM_WAIT_VALUE_GEQ;
-        ops.push_back(o);
-    }
-    void write(void* base, size_t off, uint32_t value) {
-        CUstreamBatchMemOpParams o;
-        std::memset(&o, 0, sizeof(o));
-        o.writeValue.operation = CU_STREAM_MEM_OP_WRITE_VALUE_32;
-        o.writeValue.address = reinterpret_cast<CUdeviceptr>(static_cast<char*>(base) + off);
-        o.writeValue.value = value;
-        o.writeValue.flags = 0;
-        ops.push_back(o);
-    }
-    int flush(b200_stream stream, const char* what) {
-        if (ops.empty()) return B200_OK;
-        BatchFn fn = batch_fn();
-        if (!fn) return fail(B200_CUDA_ERROR, "cuStreamBatchMemOp entry point not found");
-        for (size_t i = 0; i < ops.size(); i += 128) {
-            const unsigned n = static_cast<unsigned>(std::min<size_t>(128, ops.size() - i));
-            CUresult r = fn(static_cast<CUstream>(stream), n, ops.data() + i, 0);
-            if (r != CUDA_SUCCESS)
-                return fail(B200_CUDA_ERROR, std::string("cuStreamBatchMemOp failed for ") + what + " (CUresult " +
-                                                 std::to_string(static_cast<int>(r)) + ")");
-        }
-        ops.clear();
-        return B200_OK;
-    }
-};
-
-}  // namespace
-
-extern "C" {
-
-int b200_p2p_begin(int rank, int world, void* const* flag_peers, uint32_t epoch, b200_stream compute,
-                   b200_stream scatter, b200_stream gather) {
-    if (world < 2 || world > 64 || rank < 0 || rank >= world || !flag_peers) return fail(B200_INVALID_ARG, "p2p_begin: bad rank / world");
-    int rc;
-    MemOps tell;
-    for (int g = 0; g < world; ++g)
-        if (g != rank) tell.write(flag_peers[g], word_done(rank), epoch);
-    if ((rc = tell.flush(compute, "done flags"))) return rc;
-    for (int which = 0; which < 2; ++which) {
-        if (which == 0 && rank != 0) continue;  // only rank 0 scatters
-        MemOps hear;
-        for (int g = 0; g < world; ++g)
-            if (g != rank) hear.wait(flag_peers[rank], word_done(g), epoch);
-        if ((rc = hear.flush(which == 0 ? scatter : gather, "done waits"))) return rc;
-    }
-    return B200_OK;
-}
-
-int b200_p2p_exchange(int rank, int world, int64_t M, const int64_t* sub_cols, int p0, int p1, void* const* a_peers,
-                      void* const* flag_peers, uint32_t epoch, b200_stream compute, b200_stream scatter,
-                      b200_stream gather, uint32_t* gate_words) {
-    if (world < 2 || world > 64 || rank < 0 || rank >= world || !a_peers || !flag_peers || !sub_cols)
-        return fail(B200_INVALID_ARG, "p2p_exchange: bad rank / world / tables");
-    if (p0 < 0 || p1 > 32 || p0 > p1 || M <= 0) return fail(B200_INVALID_ARG, "p2p_exchange: bad panel range");
-    int rc;
-    auto copy_cols = [&](int dst, int64_t c0, int64_t c1, b200_stream st) -> int {
-        if (c1 <= c0) return B200_OK;
-        char* d = static_cast<char*>(a_peers[dst]) + 2 * c0 * M;
-        const char* s = static_cast<const char*>(a_peers[rank]) + 2 * c0 * M;
-        B200_CUDA_TRY(cudaMemcpyAsync(d, s, static_cast<size_t>(2 * (c1 - c0) * M), cudaMemcpyDefault, static_cast<cudaStream_t>(st)));
-        return B200_OK;
-    };
-    for (int p = p0; p < p1; ++p) {
-        const int64_t* sub = sub_cols + static_cast<size_t>(p) * world * 2;
-        if (rank == 0) {  // scatter: sub-block g goes to rank g
-            MemOps done;
-            for (int g = 1; g < world; ++g) {
-                if ((rc = copy_cols(g, sub[2 * g], sub[2 * g + 1], scatter))) return rc;
-                done.write(flag_peers[g], word_scat(p), epoch);
-            }
-            if ((rc = done.flush(scatter, "scatter flags"))) return rc;
-        } else {          // my sub-block must be here before I can pass it on
-            MemOps got;
-            got.wait(flag_peers[rank], word_scat(p), epoch);
-            if ((rc = got.flush(gather, "scatter wait"))) return rc;
-        }
-        {   // all-gather: my sub-block goes to everybody but rank 0, which has all of A
-            MemOps done;
-            // destinations are visited starting after this rank, so that at any moment the senders
-            // aim at different receivers instead of all at the same one
-            for (int i = 1; i < world; ++i) {
-                const int h = (rank + i) % world;
-                if (h == 0) continue;
-                if ((rc = copy_cols(h, sub[2 * rank], sub[2 * rank + 1], gather))) return rc;
-                done.write(flag_peers[h], word_gath(p, rank), epoch);
-            }
-            if ((rc = done.flush(gather, "all-gather flags"))) return rc;
-        }
-        if (rank != 0) {
-            // arrival of panel p on this rank: my own sub-block (scatter) and everybody else's
-            MemOps here;
-            here.wait(flag_peers[rank], word_scat(p), epoch);
-            for (int g = 0; g < world; ++g)
-                if (g != rank) here.wait(flag_peers[rank], word_gath(p, g), epoch);
-            if (gate_words) {
-                MemOps gate = here;
-                gate.write(gate_words, 4u * static_cast<size_t>(p), 1u);
-                if ((rc = gate.flush(gather, "panel gate"))) return rc;
-            }
-            if ((rc = here.flush(compute, "panel waits"))) return rc;
-        }
-    }
-    return B200_OK;
-}
-
 int b200_gemm_f16f32_host(b200_handle* h, int transA, int transB, int64_t M, int64_t N, int64_t K, float alpha,
                           const void* A, int64_t lda, const void* B, int64_t ldb, float beta, const float* C,
                           int64_t ldc, float* D, int64_t ldd) {
@@ -640,39 +532,62 @@ int b200_gemm_f16f32_host(b200_handle* h, int transA, int transB, int64_t M, int
     // The link is full duplex and the GEMM is far faster than either direction, so the call is
     // cut into column slabs: while slab j multiplies, slab j+1's B and C columns are still
     // arriving and slab j-1's D columns are already on their way back.  A is needed by every
-    // slab and goes first.
-    int slabs = static_cast<int>(std::min<int64_t>(8, (N + 511) / 512));
-    if (slabs < 1) slabs = 1;
-    const int64_t per = ((N + slabs - 1) / slabs + 255) / 256 * 256;  // whole tiles per slab
+    // slab and goes first.  The uploads keep their direction of the link busy from the first byte
+    // to the last, so what the call adds to them is whatever is left to do after the last upload:
+    // the last slabs shrink (by a third each, down to one tile) to make that one narrow product and
+    // one narrow download; a slab's download (4 bytes per element of D) then still ends before the
+    // next slab's upload (6 bytes per element for B and C) does.
+    std::vector<int64_t> widths;
+    {
+        const int64_t cap = std::max<int64_t>(256, ((N + 7) / 8 + 255) / 256 * 256);
+        int64_t left = N, w = 256;
+        while (left > 0) {
+            const int64_t take = (left <= w + w / 4) ? left : w;
+            widths.push_back(take);
+            left -= take;
+            w = std::min<int64_t>(cap, (w * 3 / 2 + 255) / 256 * 256);
+        }
+        std::reverse(widths.begin(), widths.end());
+    }
+    const int slabs = static_cast<int>(widths.size());
     while (static_cast<int>(h->events.size()) < 2 * slabs + 1) {
         cudaEvent_t e;
         B200_CUDA_TRY(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
         h->events.push_back(e);
     }
-    if (K > 0) B200_CUDA_TRY(cudaMemcpyAsync(dA, A, a_bytes, cudaMemcpyHostToDevice, s_up));
+    // Host matrices are read window by window: a column-major operand with ld > rows only has
+    // ld * (cols - 1) + rows elements, so whole-buffer copies of ld * cols would run past its end.
+    auto upload = [&](void* dst, const void* src, int64_t rows, int64_t cols, int64_t ld, int elem) -> int {
+        if (rows <= 0 || cols <= 0) return B200_OK;
+        if (ld == rows) {
+            B200_CUDA_TRY(cudaMemcpyAsync(dst, src, static_cast<size_t>(rows) * cols * elem, cudaMemcpyHostToDevice, s_up));
+        } else {
+            B200_CUDA_TRY(cudaMemcpy2DAsync(dst, static_cast<size_t>(ld) * elem, src, static_cast<size_t>(ld) * elem,
+                                            static_cast<size_t>(rows) * elem, static_cast<size_t>(cols), cudaMemcpyHostToDevice, s_up));
+        }
+        return B200_OK;
+    };
+    if (K > 0 && (rc = upload(dA, A, transA ? K : M, a_cols, lda, 2))) return rc;
     B200_CUDA_TRY(cudaEventRecord(h->events[0], s_up));
     B200_CUDA_TRY(cudaStreamWaitEvent(s_mm, h->events[0], 0));
-    int j = 0;
-    for (int64_t n0 = 0; n0 < N; n0 += per, ++j) {
-        const int64_t nc = std::min<int64_t>(per, N - n0);
+    int64_t n0 = 0;
+    for (int j = 0; j < slabs; n0 += widths[j], ++j) {
+        const int64_t nc = widths[j];
         if (K > 0) {
-            if (!transB) {  // K x N column-major: a column slab is contiguous
-                B200_CUDA_TRY(cudaMemcpyAsync(dB + n0 * ldb, static_cast<const __half*>(B) + n0 * ldb,
-                                              static_cast<size_t>(ldb) * nc * 2, cudaMemcpyHostToDevice, s_up));
+            if (!transB) {  // K x N column-major: columns n0 .. n0+nc
+                if ((rc = upload(dB + n0 * ldb, static_cast<const __half*>(B) + n0 * ldb, K, nc, ldb, 2))) return rc;
             } else {        // stored N x K: rows n0 .. n0+nc of every column
                 B200_CUDA_TRY(cudaMemcpy2DAsync(dB + n0, static_cast<size_t>(ldb) * 2, static_cast<const __half*>(B) + n0,
                                                 static_cast<size_t>(ldb) * 2, static_cast<size_t>(nc) * 2,
                                                 static_cast<size_t>(K), cudaMemcpyHostToDevice, s_up));
             }
         }
-        if (has_c)
-            B200_CUDA_TRY(cudaMemcpyAsync(dC + n0 * ldc, C + n0 * ldc, static_cast<size_t>(ldc) * nc * 4,
-                                          cudaMemcpyHostToDevice, s_up));
+        if (has_c && (rc = upload(dC + n0 * ldc, C + n0 * ldc, M, nc, ldc, 4))) return rc;
         B200_CUDA_TRY(cudaEventRecord(h->events[1 + 2 * j], s_up));
         B200_CUDA_TRY(cudaStreamWaitEvent(s_mm, h->events[1 + 2 * j], 0));
         GemmProblem g{transA, transB, M, nc, K, alpha, beta, dA, lda, transB ? dB + n0 : dB + n0 * ldb, ldb,
                       dC + n0 * ldc, ldc, dD + n0 * ldd, ldd};
-        if ((rc = run_gemm(h, s_mm, g))) return rc;
+        if ((rc = gemm_dispatch(h, s_mm, g))) return rc;
         B200_CUDA_TRY(cudaEventRecord(h->events[2 + 2 * j], s_mm));
         B200_CUDA_TRY(cudaStreamWaitEvent(s_dn, h->events[2 + 2 * j], 0));
         if (ldd == M) {

@@ -3,6 +3,7 @@
 
 #include <cudaTypedefs.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "internal.h"
@@ -35,9 +36,61 @@ struct BatchDim {
 
 // Tensor map over a column-major matrix: dim0 (contiguous) has `inner` elements, dim1 has `outer`
 // elements `ld` elements apart; batched problems add dim2 = matrix of the batch (box extent 1).
+// A tensor map is a pure function of the arguments below (it describes addresses and shapes, not
+// contents), so repeated launches on the same buffers reuse it: a small per-thread cache, most
+// recently used first.  Matters for launch-bound sizes only.
+struct MapKey {
+    const void* base;
+    int64_t inner, outer, ld, batch_count, batch_stride;
+    uint32_t box_inner, box_outer;
+    int dt, sw;
+    bool operator==(const MapKey& o) const {
+        return base == o.base && inner == o.inner && outer == o.outer && ld == o.ld && batch_count == o.batch_count &&
+               batch_stride == o.batch_stride && box_inner == o.box_inner && box_outer == o.box_outer && dt == o.dt && sw == o.sw;
+    }
+};
+struct MapCache {
+    static constexpr int kSlots = 16;
+    MapKey key[kSlots];
+    CUtensorMap map[kSlots];
+    int used = 0;
+    const CUtensorMap* find(const MapKey& k) {
+        for (int i = 0; i < used; ++i)
+            if (key[i] == k) {
+                if (i > 0) {  // move to front
+                    MapKey kk = key[i];
+                    CUtensorMap mm = map[i];
+                    for (int j = i; j > 0; --j) {
+                        key[j] = key[j - 1];
+                        map[j] = map[j - 1];
+                    }
+                    key[0] = kk;
+                    map[0] = mm;
+                }
+                return &map[0];
+            }
+        return nullptr;
+    }
+    void insert(const MapKey& k, const CUtensorMap& m) {
+        if (used < kSlots) ++used;
+        for (int j = used - 1; j > 0; --j) {
+            key[j] = key[j - 1];
+            map[j] = map[j - 1];
+        }
+        key[0] = k;
+        map[0] = m;
+    }
+};
+thread_local MapCache g_map_cache;
+
 int make_map_2d(CUtensorMap* tm, CUtensorMapDataType dt, int elem_bytes, const void* base, int64_t inner,
                 int64_t outer, int64_t ld, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle sw,
                 const char* what, BatchDim batch = BatchDim()) {
+    const MapKey mk{base, inner, outer, ld, batch.count, batch.stride, box_inner, box_outer, static_cast<int>(dt), static_cast<int>(sw)};
+    if (const CUtensorMap* hit = g_map_cache.find(mk)) {
+        *tm = *hit;
+        return B200_OK;
+    }
     EncodeFn enc = get_encode_fn();
     if (!enc) return fail(B200_CUDA_ERROR, "cuTensorMapEncodeTiled entry point not found");
     cuuint64_t dims[3] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer),
@@ -51,6 +104,21 @@ int make_map_2d(CUtensorMap* tm, CUtensorMapDataType dt, int elem_bytes, const v
     if (r != CUDA_SUCCESS)
         return fail(B200_CUDA_ERROR, std::string("cuTensorMapEncodeTiled failed for ") + what + " (CUresult " +
                                          std::to_string(static_cast<int>(r)) + ")");
+    g_map_cache.insert(mk, *tm);
+    return B200_OK;
+}
+
+// The opt-in to more than 48 KiB of dynamic shared memory is per device and per kernel: made once
+// (this also makes the driver load the kernel, which a caller may want to have happen at start-up).
+template <int kBN, bool kAMn, bool kBMn, int kCtas, bool kBatch>
+int opt_in_shared_memory() {
+    static std::atomic<uint64_t> done{0};  // bit d: device d has it
+    int dev = 0;
+    B200_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 64 && (done.load(std::memory_order_relaxed) >> dev) & 1u) return B200_OK;
+    B200_CUDA_TRY(cudaFuncSetAttribute(gemm_f16f32_tcgen05<kBN, kAMn, kBMn, kCtas, kBatch>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<kBN, kAMn, kBMn, kCtas>::SMEM_BYTES));
+    if (dev < 64) done.fetch_or(uint64_t(1) << dev, std::memory_order_relaxed);
     return B200_OK;
 }
 
@@ -59,20 +127,22 @@ int launch_kernel(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensor
                   const GemmParams& p, int grid, cudaStream_t stream) {
     using Cfg = GemmCfg<kBN, kAMn, kBMn, kCtas>;
     auto kern = gemm_f16f32_tcgen05<kBN, kAMn, kBMn, kCtas, kBatch>;
-    // per device and per function; cheap enough to repeat on every launch
-    B200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+    if (int rc = opt_in_shared_memory<kBN, kAMn, kBMn, kCtas, kBatch>()) return rc;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid, 1, 1);
     cfg.blockDim = dim3(Cfg::THREADS, 1, 1);
     cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = kCtas;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    // the kernel orders its own global accesses behind the previous kernel of the stream (griddep_wait)
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = 2;
     B200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmC, tmD, p));
     return B200_OK;
 }
@@ -119,6 +189,32 @@ Geometry geometry(const GemmProblem& g, const GemmPlan& plan) {
 }
 
 }  // namespace
+
+namespace {
+template <int kBN, int kCtas>
+int preload_layouts() {
+    int rc;
+    if ((rc = opt_in_shared_memory<kBN, false, false, kCtas, false>())) return rc;
+    if ((rc = opt_in_shared_memory<kBN, true, false, kCtas, false>())) return rc;
+    if constexpr ((kBN / kCtas) % 64 == 0) {
+        if ((rc = opt_in_shared_memory<kBN, false, true, kCtas, false>())) return rc;
+        if ((rc = opt_in_shared_memory<kBN, true, true, kCtas, false>())) return rc;
+    }
+    return B200_OK;
+}
+}  // namespace
+
+int gemm_tcgen05_preload() {
+    int rc;
+    if ((rc = preload_layouts<256, 2>())) return rc;
+    if ((rc = preload_layouts<128, 2>())) return rc;
+    if ((rc = preload_layouts<256, 1>())) return rc;
+    if ((rc = preload_layouts<128, 1>())) return rc;
+    if ((rc = preload_layouts<64, 1>())) return rc;
+    cudaFuncAttributes at;
+    B200_CUDA_TRY(cudaFuncGetAttributes(&at, gemm_splitk_reduce));
+    return B200_OK;
+}
 
 size_t gemm_tcgen05_scratch_bytes(const GemmProblem& g, const GemmPlan& plan) {
     const Geometry q = geometry(g, plan);

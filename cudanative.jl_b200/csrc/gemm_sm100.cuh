@@ -28,6 +28,10 @@
 //
 // Every barrier wait is bounded (ptx_sm100.cuh: mbar_wait); on expiry the CTA records the wait
 // in the device status word and every role falls through to the common exit.
+//
+// The kernel is launched with programmatic stream serialization: its set-up (barriers, tensor
+// memory, descriptor prefetch) runs under the tail of the previous kernel of the stream, and
+// griddepcontrol.wait orders every global access behind that kernel's completion.
 #pragma once
 
 #include "ptx_sm100.cuh"
@@ -155,6 +159,11 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     if constexpr (kPair) cluster_sync_all();  // peer barriers exist before anyone signals them
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    // Everything above touched only this CTA's own shared and tensor memory, so it may overlap the
+    // tail of the previous kernel in the stream (whose last CTAs are still finishing while this CTA
+    // already sits on an SM that has become free); global memory is touched only after the wait.
+    griddep_launch_dependents();
+    griddep_wait();
 
     // unit -> (tile row, tile col, k-block range, matrix of the batch)
     auto unit_decode = [&](int unit, int& m0, int& n0, int& kb0, int& kb1, int& out_n0, int& bz) {
@@ -225,9 +234,6 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     tma_load_2d(dst, &tmB, x, y, bar);
                 }
             };
-#ifdef B200_PROBE_SKIP_LOADS
-            uint32_t issued = 0;
-#endif
             for (int unit = unit_first; ok && unit < num_units; unit += unit_stride) {
                 int m0, n0, kb0, kb1, out_n0;
                 unit_decode(unit, m0, n0, kb0, kb1, out_n0, bz);
@@ -243,14 +249,6 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     }
                     ok = mbar_wait(empty_bar(s), ph ^ 1u, wc, kWaitEmptyStage);
                     if (!ok) break;
-#ifdef B200_PROBE_SKIP_LOADS
-                    // timing probe (results are wrong): after the ring has been filled once,
-                    // stages are handed back to the MMA without reloading them
-                    if (issued++ >= static_cast<uint32_t>(STAGES)) {
-                        if (cta_rank == 0) mbar_arrive(full_bar(s));
-                        continue;
-                    }
-#endif
                     const uint32_t sa = stages_base + s * Cfg::STAGE_BYTES;
                     const uint32_t sb = sa + Cfg::A_BYTES;
                     const int k0 = kb * Cfg::BK;
@@ -336,22 +334,12 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                         umma_f16<kCtas>(d_tmem, da + k * kStepA, db + k * kStepB, idesc, accumulate);
                         accumulate = 1u;
                     }
-#ifdef B200_DOUBLE_COMMIT
-                    umma_commit<kCtas>(empty_bar(s));
-                    if constexpr (kPair) umma_commit<kCtas>(mapa_shared(empty_bar(s), 1));
-#else
                     if constexpr (kPair) umma_commit_pair(empty_bar(s));
                     else umma_commit<kCtas>(empty_bar(s));
-#endif
                 }
                 if (!ok) break;
-#ifdef B200_DOUBLE_COMMIT
-                umma_commit<kCtas>(tmem_full_bar(acc));
-                if constexpr (kPair) umma_commit<kCtas>(mapa_shared(tmem_full_bar(acc), 1));
-#else
                 if constexpr (kPair) umma_commit_pair(tmem_full_bar(acc));
                 else umma_commit<kCtas>(tmem_full_bar(acc));
-#endif
             }
         }
         __syncwarp();

@@ -5,6 +5,7 @@
 #include <stdint.h>
 
 #include <string>
+#include <vector>
 
 #include "../../include/b200wmma.h"
 
@@ -66,6 +67,48 @@ struct LaunchInfo {
     int kernel, tile_n, split_k, ctas, cta_pair;
 };
 
+}  // namespace b200
+
+// The per-device handle behind the C ABI (opaque to callers).
+struct b200_handle {
+    int device = 0;
+    int sm_count = 0;
+    int* status_word = nullptr;  // 4 ints on the device
+    // options
+    int force_kernel = B200_KERNEL_AUTO;
+    int max_ctas = 0;
+    unsigned long long wait_budget_ns = 2000000000ull;
+    int tile_n = 0;
+    int split_k = 0;
+    int cta_pair = 0;
+    int raster_group = 0;
+    int check_on_call = 0;
+    // workspace of the host-buffer entry point and split-K scratch (grown on demand)
+    void* ws[4] = {nullptr, nullptr, nullptr, nullptr};
+    size_t ws_bytes[4] = {0, 0, 0, 0};
+    float* scratch = nullptr;
+    size_t scratch_bytes = 0;
+    cudaStream_t streams[3] = {nullptr, nullptr, nullptr};  // upload / multiply / download
+    std::vector<cudaEvent_t> events;
+    b200::LaunchInfo last = {0, 0, 0, 0, 0};
+    // "check on the next call" (B200_OPT_CHECK_ON_CALL): the stream of the previous launch, and an
+    // event recorded behind it
+    cudaEvent_t last_done = nullptr;
+    bool last_pending = false;
+    // status-word reads go through a private non-blocking stream and a page-locked word, so that they
+    // never wait for unrelated work of the caller (a plain cudaMemcpy joins the legacy default stream)
+    cudaStream_t poll_stream = nullptr;
+    int* host_word = nullptr;
+};
+
+namespace b200 {
+
+// Validate, pick a kernel and enqueue one GEMM on `stream` (the body of every GEMM entry point).
+int gemm_dispatch(b200_handle* h, cudaStream_t stream, const GemmProblem& g);
+int check_current_device(const b200_handle* h);
+// Copies the handle's 4-int device status word to `word` (synchronous) and clears it when non-zero.
+int read_status(b200_handle* h, int* word);
+
 // Scratch needed for the plan's split-K partials, in bytes (0 when split_k == 1).
 size_t gemm_tcgen05_scratch_bytes(const GemmProblem& g, const GemmPlan& plan);
 
@@ -75,6 +118,10 @@ bool gemm_tcgen05_eligible(const GemmProblem& g, std::string* why);
 // Enqueue the tcgen05 GEMM (and the split-K reduction when plan.split_k > 1).
 int gemm_tcgen05_launch(const GemmProblem& g, const GemmPlan& plan, float* scratch, int* status_word,
                         int sm_count, cudaStream_t stream, LaunchInfo* info);
+
+// Loads every non-batched instantiation of the tcgen05 kernel and the split-K reduction on the current
+// device and opts them in to their shared memory, so that no later launch does it.
+int gemm_tcgen05_preload();
 
 // Enqueue the plain shared-memory kernel: any shape, any alignment.
 int gemm_simple_launch(const GemmProblem& g, cudaStream_t stream, LaunchInfo* info);

@@ -21,16 +21,23 @@
 // that first call outside of any stream capture.
 //
 // All calls on one device share the array and it keeps whatever the previous call left there.
-// The status word is cleared (on the caller's stream) at the start of every call; the partials
-// need no clearing because every slice writes its whole window before the reduction reads it.
+// The partials need no clearing because every slice writes its whole window before the reduction
+// reads it.  The status word is cleared by whoever reads it (a synchronous call, or
+// b200_static_status); an asynchronous caller that never asks keeps the first failure on record.
 // Two calls that overlap on the GPU (different streams, or different threads) race on the array:
 // serialise them.
+//
+// "Allocates nothing" has one more condition: the first launch of a kernel makes the driver load
+// it, and loading allocates.  b200_static_warmup does all of that up front (symbol lookup, every
+// kernel variant the entry point can pick); call it once per device at start-up, outside of any
+// stream capture, and nothing after it allocates.
 #include <cuda_runtime.h>
 
 #include <mutex>
 #include <string>
 
 #include "internal.h"
+#include "ptx_sm100.cuh"
 
 namespace {
 
@@ -40,6 +47,21 @@ constexpr size_t kHeaderBytes = 256;
 constexpr size_t kPartialBytes = 16u << 20;
 
 static __device__ __align__(256) unsigned char g_static_scratch[kHeaderBytes + kPartialBytes];
+
+// One warp waits, with a budget, on a barrier nothing ever arrives on, and reports into the static
+// status word: the way to see b200_static_status work without any fault, trap or endless loop.
+__global__ void static_selftest_kernel(int* status, unsigned long long budget_ns) {
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        b200::mbar_init(b200::smem_u32(&bar), 1);
+        b200::fence_mbar_init();
+    }
+    __syncthreads();
+    b200::WaitCtx wc{&abort_flag, status, budget_ns};
+    b200::mbar_wait(b200::smem_u32(&bar), 0, wc, b200::kWaitSelftest);
+}
 
 constexpr int kMaxDevices = 64;
 std::mutex g_mutex;
@@ -88,7 +110,8 @@ extern "C" int b200_gemm_f16f32_splitk_static(b200_stream stream, int transA, in
     if (!gemm_tcgen05_eligible(g, &why)) return fail(B200_UNSUPPORTED, "static split-K gemm: " + why);
     GemmPlan plan = {};
     plan.tile_n = N > 128 ? 256 : (N > 64 ? 128 : 64);
-    plan.cta_pair = 1;
+    // the handle path's tile choice: 2-CTA tiles once the tile is 256 columns wide and there are rows enough
+    plan.cta_pair = (M > 128 && plan.tile_n == 256) ? 2 : 1;
     plan.split_k = split_k;
     plan.max_ctas = 0;
     plan.raster_group = 0;
@@ -105,7 +128,6 @@ extern "C" int b200_gemm_f16f32_splitk_static(b200_stream stream, int transA, in
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     int* status = reinterpret_cast<int*>(base);
     float* partials = reinterpret_cast<float*>(base + kHeaderBytes);
-    B200_CUDA_TRY(cudaMemsetAsync(status, 0, 4 * sizeof(int), s));
     if (need == 0) {
         // K is too short to cut: a single slice needs no partials, only the status word
         plan.split_k = 1;
@@ -115,9 +137,48 @@ extern "C" int b200_gemm_f16f32_splitk_static(b200_stream stream, int transA, in
         B200_CUDA_TRY(cudaStreamSynchronize(s));
         int word[4] = {0, 0, 0, 0};
         B200_CUDA_TRY(cudaMemcpy(word, status, sizeof(word), cudaMemcpyDeviceToHost));
+        if (word[0] != 0) B200_CUDA_TRY(cudaMemset(status, 0, sizeof(word)));
         if (word[0] != 0)
             return fail(B200_DEVICE_TIMEOUT, "static split-K gemm: a bounded wait ran out on the device (wait id " +
                                                  std::to_string(word[0]) + ", block " + std::to_string(word[1]) + ")");
     }
+    return B200_OK;
+}
+
+extern "C" int b200_static_status(int* code, int* block, int* detail) {
+    unsigned char* base = nullptr;
+    int sm_count = 0;
+    int rc = static_scratch(&base, &sm_count);
+    if (rc) return rc;
+    int word[4] = {0, 0, 0, 0};
+    B200_CUDA_TRY(cudaMemcpy(word, base, sizeof(word), cudaMemcpyDeviceToHost));
+    if (word[0] != 0) B200_CUDA_TRY(cudaMemset(base, 0, sizeof(word)));
+    if (code) *code = word[0];
+    if (block) *block = word[1];
+    if (detail) *detail = word[2];
+    return B200_OK;
+}
+
+extern "C" int b200_static_warmup(void) {
+    unsigned char* base = nullptr;
+    int sm_count = 0;
+    int rc = static_scratch(&base, &sm_count);
+    if (rc) return rc;
+    if ((rc = b200::gemm_tcgen05_preload())) return rc;
+    // the array is zero-initialised when the module is loaded; make sure of the status word anyway
+    B200_CUDA_TRY(cudaMemset(base, 0, 4 * sizeof(int)));
+    return B200_OK;
+}
+
+extern "C" int b200_static_selftest_bounded_wait(b200_stream stream, int64_t budget_ns) {
+    if (budget_ns < 1000 || budget_ns > 1000000000ll)
+        return b200::fail(B200_INVALID_ARG, "selftest budget must be within [1 us, 1 s]");
+    unsigned char* base = nullptr;
+    int sm_count = 0;
+    int rc = static_scratch(&base, &sm_count);
+    if (rc) return rc;
+    static_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(reinterpret_cast<int*>(base),
+                                                                            static_cast<unsigned long long>(budget_ns));
+    B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
 }

@@ -199,6 +199,17 @@ __device__ __forceinline__ void cluster_sync_all() {
 }
 
 // ---------------------------------------------------------------------------------------------
+// programmatic dependent launch
+// ---------------------------------------------------------------------------------------------
+// A kernel launched with the programmatic-stream-serialization attribute may start while the kernel
+// before it in the stream is still running.  griddep_wait() returns once that kernel has completed
+// and its memory operations are visible: nothing that reads or writes global memory may come before
+// it.  griddep_launch_dependents() tells the scheduler that the NEXT kernel in the stream may be
+// brought onto SMs as they free up.  Both are no-ops for a kernel launched the ordinary way.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// ---------------------------------------------------------------------------------------------
 // TMA
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* tm) {

@@ -219,4 +219,120 @@ function gemm_host!(h::Handle, D::Matrix{Float32}, A::Matrix{Float16}, B::Matrix
     return D
 end
 
+"""
+    gemm_typed!(h, D, A, B, C; c_type, d_type, ...)
+
+`gemm!` with Float16 or Float32 C and D chosen independently (b200_gemm_f16_typed): the four accumulator / result
+type combinations of `Config{16, 16, 16, d_type}` and `load_c` (src/device/cuda/wmma.jl:23-30).
+"""
+function gemm_typed!(h::Handle, D, A, B, C = nothing; c_type = ELEM_F32, d_type = ELEM_F32, alpha = 1f0, beta = 0f0,
+                     transA = false, transB = false, stream::CuStream = CuDefaultStream())
+    M, K = transA ? (A.cols, A.rows) : (A.rows, A.cols)
+    N = transB ? B.rows : B.cols
+    check(ccall((:b200_gemm_f16_typed, lib), Cint,
+                (Ptr{Cvoid}, Ptr{Cvoid}, Cint, Cint, Int64, Int64, Int64, Cfloat, CuPtr{Cvoid}, Int64, CuPtr{Cvoid}, Int64,
+                 Cfloat, CuPtr{Cvoid}, Int64, Cint, CuPtr{Cvoid}, Int64, Cint),
+                h.ptr, stream.handle, transA, transB, M, N, K, alpha, A.ptr, A.ld, B.ptr, B.ld, beta,
+                C === nothing ? CuPtr{Cvoid}(0) : C.ptr, C === nothing ? M : C.ld, c_type, D.ptr, D.ld, d_type))
+end
+
+"""
+    gemm_gated!(h, D, A, B, C, panel_flags, panel_k; ...)
+
+`gemm!` whose main loop reads columns `[j*panel_k, (j+1)*panel_k)` of A only once the 32-bit device word
+`panel_flags[j]` is non-zero (b200_gemm_f16f32_gated): one launch that overlaps the arrival of A.
+"""
+function gemm_gated!(h::Handle, D, A, B, C, panel_flags::CuPtr{UInt32}, panel_k::Integer; alpha = 1f0, beta = 0f0,
+                     transA = false, transB = false, stream::CuStream = CuDefaultStream())
+    M, K = transA ? (A.cols, A.rows) : (A.rows, A.cols)
+    N = transB ? B.rows : B.cols
+    check(ccall((:b200_gemm_f16f32_gated, lib), Cint,
+                (Ptr{Cvoid}, Ptr{Cvoid}, Cint, Cint, Int64, Int64, Int64, Cfloat, CuPtr{Cvoid}, Int64, CuPtr{Cvoid}, Int64,
+                 Cfloat, CuPtr{Cvoid}, Int64, CuPtr{Cvoid}, Int64, CuPtr{UInt32}, Int64),
+                h.ptr, stream.handle, transA, transB, M, N, K, alpha, A.ptr, A.ld, B.ptr, B.ld, beta,
+                C === nothing ? CuPtr{Cvoid}(0) : C.ptr, C === nothing ? M : C.ld, D.ptr, D.ld, panel_flags, panel_k))
+end
+
+# ---- the allocation-free split-K product (no handle) -------------------------------------------------
+"Once per device at start-up: address lookup and kernel loading for `gemm_splitk_static!` (b200_static_warmup)."
+static_warmup() = check(ccall((:b200_static_warmup, lib), Cint, ()))
+
+"`(code, block, detail)` of the static entry point's device status word; clears it (b200_static_status)."
+function static_status()
+    code, block, detail = Ref{Cint}(0), Ref{Cint}(0), Ref{Cint}(0)
+    check(ccall((:b200_static_status, lib), Cint, (Ptr{Cint}, Ptr{Cint}, Ptr{Cint}), code, block, detail))
+    return (code[], block[], detail[])
+end
+
+"""
+    gemm_splitk_static!(D, A, B, C; split_k, sync = true, ...)
+
+The product for callers that must not allocate device memory when they need it (b200_gemm_f16f32_splitk_static):
+partial products live in a 16 MiB array inside the library image; calls on one device must not overlap.
+"""
+function gemm_splitk_static!(D, A, B, C = nothing; split_k = 2, sync = true, alpha = 1f0, beta = 0f0, transA = false,
+                             transB = false, stream::CuStream = CuDefaultStream())
+    M, K = transA ? (A.cols, A.rows) : (A.rows, A.cols)
+    N = transB ? B.rows : B.cols
+    check(ccall((:b200_gemm_f16f32_splitk_static, lib), Cint,
+                (Ptr{Cvoid}, Cint, Cint, Int64, Int64, Int64, Cfloat, CuPtr{Cvoid}, Int64, CuPtr{Cvoid}, Int64, Cfloat,
+                 CuPtr{Cvoid}, Int64, CuPtr{Cvoid}, Int64, Cint, Cint),
+                stream.handle, transA, transB, M, N, K, alpha, A.ptr, A.ld, B.ptr, B.ld, beta,
+                C === nothing ? CuPtr{Cvoid}(0) : C.ptr, C === nothing ? M : C.ld, D.ptr, D.ld, split_k, sync ? 1 : 0))
+end
+
+# ---- N-sharded multi-GPU GEMM: one Julia process (or task) per device ------------------------------
+const SHARDED_BLOB_BYTES = 128
+const SHARDED_GATED, SHARDED_NO_TRANSFER = Cint(1), Cint(2)
+
+"""
+    Sharded(h, rank, world, M, N, K; panels = 16, exchange)
+
+One rank of `D[:, slab_r] = alpha * A * B[:, slab_r] + beta * C[:, slab_r]` (b200_sharded_*).  `exchange` takes this
+rank's 128-byte blob and returns the concatenation of every rank's blobs in rank order, e.g.
+`blob -> MPI.Allgather(blob, comm)`.  `s.a` is this rank's A buffer (M x K Float16, valid on rank 0 before a product,
+everywhere after it); `s.n0:s.n1-1` (0-based) are this rank's columns of B, C and D.
+"""
+mutable struct Sharded
+    ptr::Ptr{Cvoid}
+    a::CuPtr{Float16}
+    n0::Int64
+    n1::Int64
+    function Sharded(h::Handle, rank::Integer, world::Integer, M::Integer, N::Integer, K::Integer; panels::Integer = 16,
+                     exchange = nothing)
+        p = Ref{Ptr{Cvoid}}(C_NULL)
+        check(ccall((:b200_sharded_create, lib), Cint, (Ptr{Ptr{Cvoid}}, Ptr{Cvoid}, Cint, Cint, Int64, Int64, Int64, Cint),
+                    p, h.ptr, rank, world, M, N, K, panels))
+        n0, n1 = Ref{Int64}(0), Ref{Int64}(0)
+        a, flags = Ref{Ptr{Cvoid}}(C_NULL), Ref{Ptr{Cvoid}}(C_NULL)
+        np, ng = Ref{Cint}(0), Ref{Cint}(0)
+        check(ccall((:b200_sharded_info, lib), Cint,
+                    (Ptr{Cvoid}, Ptr{Int64}, Ptr{Int64}, Ptr{Ptr{Cvoid}}, Ptr{Ptr{Cvoid}}, Ptr{Cint}, Ptr{Cint}),
+                    p[], n0, n1, a, flags, np, ng))
+        if world > 1
+            blob = zeros(UInt8, SHARDED_BLOB_BYTES)
+            check(ccall((:b200_sharded_ipc_blob, lib), Cint, (Ptr{Cvoid}, Ptr{UInt8}), p[], blob))
+            blobs = exchange(blob)::Vector{UInt8}
+            length(blobs) == world * SHARDED_BLOB_BYTES || error("exchange must return one 128-byte blob per rank")
+            check(ccall((:b200_sharded_attach, lib), Cint, (Ptr{Cvoid}, Ptr{UInt8}), p[], blobs))
+        end
+        s = new(p[], reinterpret(CuPtr{Float16}, a[]), n0[], n1[])
+        finalizer(x -> ccall((:b200_sharded_destroy, lib), Cint, (Ptr{Cvoid},), x.ptr), s)
+        return s
+    end
+end
+
+"Enqueue one product on `stream` (b200_sharded_run); every rank must make the call."
+function run!(s::Sharded, D_slab, B_slab, C_slab = nothing; alpha = 1f0, beta = 0f0, flags = Cint(0),
+              stream::CuStream = CuDefaultStream())
+    check(ccall((:b200_sharded_run, lib), Cint,
+                (Ptr{Cvoid}, Ptr{Cvoid}, Cfloat, CuPtr{Cvoid}, Int64, Cfloat, CuPtr{Cvoid}, Int64, CuPtr{Cvoid}, Int64, Cint),
+                s.ptr, stream.handle, alpha, B_slab.ptr, B_slab.ld, beta,
+                C_slab === nothing ? CuPtr{Cvoid}(0) : C_slab.ptr, C_slab === nothing ? D_slab.ld : C_slab.ld,
+                D_slab.ptr, D_slab.ld, flags))
+end
+
+"Host-side wait with a deadline (b200_sharded_wait): throws B200Error(6, ...) when a peer never wrote its flags."
+wait!(s::Sharded, timeout_ms::Integer = 60000) = check(ccall((:b200_sharded_wait, lib), Cint, (Ptr{Cvoid}, Int64), s.ptr, timeout_ms))
+
 end # module

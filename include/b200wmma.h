@@ -30,7 +30,8 @@ enum {
     B200_UNSUPPORTED = 2,    /* legal request this build has no kernel for                       */
     B200_CUDA_ERROR = 3,     /* a CUDA runtime / driver call failed; text in b200_last_error()   */
     B200_DEVICE_TIMEOUT = 4, /* a bounded wait inside a kernel ran out; see b200_device_status() */
-    B200_NO_DEVICE = 5       /* no CUDA device, or the device is not compute capability 10.x     */
+    B200_NO_DEVICE = 5,      /* no CUDA device, or the device is not compute capability 10.x     */
+    B200_PEER_TIMEOUT = 6    /* sharded GEMM: a peer's flag write did not arrive within the deadline */
 };
 
 /* Layout tags: the reference's WMMA.ColMajor / WMMA.RowMajor (src/device/cuda/wmma.jl:313-338). */
@@ -64,7 +65,12 @@ enum {
     B200_OPT_TILE_N = 3,         /* 0 = auto, else 64 / 128 / 256                                 */
     B200_OPT_SPLIT_K = 4,        /* 0 = auto, 1 = off, n>1 = split the K loop n ways              */
     B200_OPT_CTA_PAIR = 5,       /* 0 = auto, 1 = one-CTA tiles only, 2 = force 2-CTA tiles       */
-    B200_OPT_RASTER_GROUP = 6    /* tile rows per rasterisation group (0 = default)               */
+    B200_OPT_RASTER_GROUP = 6,   /* tile rows per rasterisation group (0 = default)               */
+    B200_OPT_CHECK_ON_CALL = 7   /* 1 = every GEMM entry point first looks at the status word of the  */
+                                 /* handle's previous launch, if that launch has finished, and returns */
+                                 /* B200_DEVICE_TIMEOUT when a wait ran out in it: the reference polls */
+                                 /* its device exception flag the same way at every API call          */
+                                 /* (src/init.jl:37, src/exceptions.jl:76-89).  Default 0.            */
 };
 
 typedef struct b200_handle b200_handle;
@@ -219,12 +225,30 @@ int b200_gemm_f16f32_host(b200_handle* h, int transA, int transB, int64_t M, int
  *   - The first call on a device looks the array's address up; make it outside stream capture.
  *   - All calls on a device share the array: calls that overlap on the GPU race.  Serialise them.
  *   - sync_and_check != 0: synchronise the stream and return B200_DEVICE_TIMEOUT if a bounded
- *     wait ran out; 0: return as soon as the work is enqueued. */
+ *     wait ran out; 0: return as soon as the work is enqueued (then ask b200_static_status).
+ *   - The first launch of each kernel variant makes the driver load it, which allocates: call
+ *     b200_static_warmup at start-up if even that must not happen later. */
 int b200_gemm_f16f32_splitk_static(b200_stream stream, int transA, int transB, int64_t M,
                                    int64_t N, int64_t K, float alpha, const void* A, int64_t lda,
                                    const void* B, int64_t ldb, float beta, const float* C,
                                    int64_t ldc, float* D, int64_t ldd, int split_k,
                                    int sync_and_check);
+
+/* Companions of b200_gemm_f16f32_splitk_static; like it they have no counterpart in the reference
+ * and call no cudaMalloc / cudaFree.
+ *
+ * b200_static_warmup: once per device at start-up, outside stream capture.  Looks the static
+ *   array's address up and makes the driver load every kernel variant the static entry point can
+ *   pick (loading a kernel for its first launch is the one thing that would still allocate later).
+ * b200_static_status: the device status word of the static entry point on the current device:
+ *   code 0 = nothing, else the id of the wait that ran out, its block and a detail word; clears
+ *   the word.  A caller that passes sync_and_check = 0 calls this after it has synchronised, and
+ *   before results are used; the word keeps the first failure until somebody reads it.
+ * b200_static_selftest_bounded_wait: one warp waits with the given budget (1 us .. 1 s) on a
+ *   barrier nothing signals and reports into the static status word (wait id 107). */
+int b200_static_warmup(void);
+int b200_static_status(int* code, int* block, int* detail);
+int b200_static_selftest_bounded_wait(b200_stream stream, int64_t budget_ns);
 
 /* ------------------------------------------------------------------------------------------ */
 /* the 16x16x16 unit: one WMMA multiply-accumulate                                             */
@@ -298,32 +322,88 @@ int b200_ipc_open_handle(const void* handle64, void** dptr);
 int b200_ipc_close_handle(void* dptr);
 int b200_memcpy_d2d(void* dst, const void* src, size_t bytes, b200_stream stream);
 
-/* Transfer schedule of the N-sharded GEMM (no counterpart in the reference).  A (M rows,
- * column-major, binary16) starts on rank 0 and travels in K panels: rank 0 copies sub-block g of
- * a panel into rank g's A (scatter), every rank then copies its own sub-block into every other
- * rank's A (all-gather); copies run on the copy engines.  Behind each copy the sending stream
- * writes `epoch` into a flag word in the receiver's flag block, and receiving streams wait for
- * those words (stream memory operations; no kernel, no SM).
+/* ------------------------------------------------------------------------------------------ */
+/* N-sharded multi-GPU GEMM, one object per rank                                               */
+/* ------------------------------------------------------------------------------------------ */
+
+/*     D[:, slab_r] = alpha * A * B[:, slab_r] + beta * C[:, slab_r]        on every rank r
  *
- * a_peers / flag_peers: `world` device addresses, entry r = this rank's own buffers, the others
- * IPC-mapped.  The flag block is B200_P2P_FLAG_BYTES of zero-initialised device memory.
- * sub_cols: for every panel p and rank g the column range [c0, c1) of sub-block g, as
- * sub_cols[(p * world + g) * 2 + {0, 1}].
+ * No counterpart in the reference, which computes on one device per task (src/init.jl:187-209).
+ * What is kept from it: raw device pointers that the caller owns, the way a CuArray converts for
+ * ccall (src/array.jl:15); asynchronous enqueue on the caller's stream (src/execution.jl:158-166);
+ * one process (or task) per device.
  *
- * b200_p2p_begin   : once per product, first: announces on `compute` that this rank no longer
- *                    touches its A from earlier work and makes `scatter` (rank 0) and `gather`
- *                    wait until every peer has announced the same for `epoch`.
- * b200_p2p_exchange: enqueues the copies and flag writes of panels [p0, p1) on `scatter` /
- *                    `gather`, and on `compute` the waits for the arrival of those panels here.
- *                    gate_words != NULL additionally writes 1 to gate_words[p] on `gather` once
- *                    panel p is complete here (the flags b200_gemm_f16f32_gated polls). */
-#define B200_P2P_FLAG_BYTES (4 * (128 + 32 * 64))
-int b200_p2p_begin(int rank, int world, void* const* flag_peers, uint32_t epoch, b200_stream compute,
-                   b200_stream scatter, b200_stream gather);
-int b200_p2p_exchange(int rank, int world, int64_t M, const int64_t* sub_cols, int p0, int p1,
-                      void* const* a_peers, void* const* flag_peers, uint32_t epoch,
-                      b200_stream compute, b200_stream scatter, b200_stream gather,
-                      uint32_t* gate_words);
+ * B, C and D are split into contiguous column slabs (whole 256-column tiles per rank) that never
+ * move.  A (M x K, column-major, lda = M, binary16) lives in a buffer the object owns on every
+ * rank; before a product its contents are valid on rank 0 only, afterwards everywhere.  It
+ * travels in K panels over NVLink on the copy engines (scatter from rank 0, then all-gather
+ * among the receivers), ordered by stream memory operations on flag words; the GEMM runs as a
+ * few launches over growing K ranges, each behind the arrival of its own panels only.
+ *
+ * Life cycle, on every rank, in this order:
+ *   b200_sharded_create     allocates A and the flag block on the handle's device
+ *   b200_sharded_ipc_blob   128 bytes that let another process map both
+ *   (the caller moves every rank's blob to every rank: MPI, files, sockets, torch.distributed)
+ *   b200_sharded_attach     maps the peers' buffers; `blobs` = world x 128 bytes, entry r from rank r
+ *     or b200_sharded_attach_local for peers that live in THIS process (one process driving
+ *     several devices): entry r = rank r's A and flag block as b200_sharded_info returns them
+ *   b200_sharded_run        once per product; every rank must make the same sequence of calls
+ *   b200_sharded_wait       host-side wait with a deadline (optional; see below)
+ *   b200_sharded_destroy    after every rank has synchronised its last product
+ */
+typedef struct b200_sharded b200_sharded;
+
+#define B200_SHARDED_MAX_RANKS 64
+#define B200_SHARDED_MAX_PANELS 32
+#define B200_SHARDED_BLOB_BYTES 128
+#define B200_SHARDED_FLAG_BYTES (4 * (128 + 32 * 64))
+
+/* flags of b200_sharded_run */
+enum {
+    B200_SHARDED_GATED = 1,       /* ONE launch of the gated GEMM (b200_gemm_f16f32_gated) instead of a
+                                     few launches: overlaps transfer and main loop inside the kernel  */
+    B200_SHARDED_NO_TRANSFER = 2  /* A is already valid on this rank: the same launches without any copy
+                                     or wait (the compute-only time of a product)                     */
+};
+
+int b200_sharded_create(b200_sharded** out, b200_handle* h, int rank, int world, int64_t M, int64_t N,
+                        int64_t K, int panels);
+int b200_sharded_destroy(b200_sharded* s);
+
+/* This rank's column slab [n0, n1) of B / C / D, its A buffer (M * K binary16) and flag block, and
+ * how many transfer panels and GEMM launches a product takes.  Any out pointer may be NULL. */
+int b200_sharded_info(b200_sharded* s, int64_t* n0, int64_t* n1, void** a, void** flags, int* n_panels,
+                      int* n_groups);
+int b200_sharded_ipc_blob(b200_sharded* s, void* blob128);
+int b200_sharded_attach(b200_sharded* s, const void* blobs);
+int b200_sharded_attach_local(b200_sharded* s, void* const* a_ptrs, void* const* flag_ptrs);
+
+/* Enqueue one product on `stream`.  B_slab: K x (n1-n0), C_slab / D_slab: M x (n1-n0), column-major
+ * device pointers with their leading dimensions; D_slab may alias C_slab.  A rank whose slab is
+ * empty still makes the call (it takes part in the transfer).  Returns as soon as the work is
+ * enqueued; a wait that ran out inside a kernel shows in b200_device_status / b200_sharded_wait. */
+int b200_sharded_run(b200_sharded* s, b200_stream stream, float alpha, const void* B_slab, int64_t ldb,
+                     float beta, const float* C_slab, int64_t ldc, float* D_slab, int64_t ldd, int flags);
+
+/* Wait on the host until the last product's work on this rank has finished, for at most
+ * timeout_ms.  The stream-level waits of the transfer have no timeout of their own: a peer that
+ * skipped the call or died would leave this rank's streams blocked for good.  On expiry this call
+ * therefore raises every flag word of this rank's own flag block itself (all stream waits look
+ * only at that block), lets the released work drain, marks the object unusable and returns
+ * B200_PEER_TIMEOUT; D is not valid then.  Otherwise B200_OK, or B200_DEVICE_TIMEOUT when a
+ * bounded wait ran out inside a kernel.  Plays the role of the reference's synchronize() plus its
+ * exception poll (src/exceptions.jl:76-89). */
+int b200_sharded_wait(b200_sharded* s, int64_t timeout_ms);
+
+/* The layout arithmetic of the above as a pure host function (no CUDA call): slab bounds
+ * (world + 1), panel bounds (*n_panels + 1), GEMM launch groups as panel bounds (*n_groups + 1) and,
+ * for every panel p and rank g, the columns [c0, c1) of A that rank g forwards:
+ * sub_cols[(p * world + g) * 2 + {0, 1}].  Arrays must hold B200_SHARDED_MAX_RANKS + 1,
+ * B200_SHARDED_MAX_PANELS + 1, B200_SHARDED_MAX_PANELS + 1 and 2 * world * B200_SHARDED_MAX_PANELS
+ * entries; any may be NULL. */
+int b200_sharded_layout(int world, int64_t N, int64_t K, int panels, int64_t* slab_bounds,
+                        int64_t* panel_bounds, int* n_panels, int* group_bounds, int* n_groups,
+                        int64_t* sub_cols);
 
 /* Counter-based synthetic matrices (no counterpart in the reference, whose tests draw from
  * Julia's unseeded rand; test/device/wmma.jl:196-199).  Element (i, j) of a rows x cols

@@ -118,7 +118,7 @@ def julia_ccalls() -> list:
 def test_julia_ccalls_match_the_header():
     protos = header_prototypes()
     calls = julia_ccalls()
-    assert len(calls) >= 16
+    assert len(calls) >= 28
     seen = set()
     for name, ret, arg_types, n_values in calls:
         want_ret, want_args = protos[name]
@@ -129,5 +129,8 @@ def test_julia_ccalls_match_the_header():
     # the entry points of the path must all be bound
     for must in ("b200_create", "b200_destroy", "b200_gemm_f16f32", "b200_gemm_f16f32_host", "b200_gemm_strided_batched",
                  "b200_wmma_load", "b200_wmma_fill_c", "b200_wmma_mma", "b200_wmma_store_d", "b200_wmma_bcast",
-                 "b200_wmma_16x16x16", "b200_last_error", "b200_malloc", "b200_free", "b200_set_option", "b200_device_status"):
+                 "b200_wmma_16x16x16", "b200_last_error", "b200_malloc", "b200_free", "b200_set_option", "b200_device_status",
+                 "b200_gemm_f16_typed", "b200_gemm_f16f32_gated", "b200_gemm_f16f32_splitk_static", "b200_static_status",
+                 "b200_static_warmup", "b200_sharded_create", "b200_sharded_info", "b200_sharded_ipc_blob",
+                 "b200_sharded_attach", "b200_sharded_run", "b200_sharded_wait", "b200_sharded_destroy"):
         assert must in seen, f"{must} has no ccall in B200WMMA.jl"

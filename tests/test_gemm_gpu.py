@@ -402,6 +402,66 @@ def test_bounded_wait_reports_and_context_survives(handle, oracle):
     oracle.assert_close(d, oracle.gemm_ref(False, False, 1.0, a, b, 1.0, c), "after timeout")
 
 
+def test_check_on_call_finds_an_earlier_failure_at_the_next_call(handle, oracle):
+    """B200_OPT_CHECK_ON_CALL: like the reference's exception flag, polled at every API call
+    (src/init.jl:37, src/exceptions.jl:76-89 of CUDAnative.jl), a wait that ran out in an earlier,
+    finished launch makes the NEXT GEMM call return B200_DEVICE_TIMEOUT without launching; the call
+    after that works.  Off by default: the same sequence then stays silent until device_status."""
+    from cudanative_jl_b200 import B200Error
+
+    L = _lib.lib()
+    force(handle, _lib.KERNEL_AUTO)
+    a, b, c = operands(128, 128, 128, False, False, seed=6)
+    want = oracle.gemm_ref(False, False, 1.0, a, b, 1.0, c)
+    handle.set_option(_lib.OPT_CHECK_ON_CALL, 1)
+    assert handle.get_option(_lib.OPT_CHECK_ON_CALL) == 1
+    d = run_gemm(handle, False, False, 128, 128, 128, 1.0, a, b, 1.0, c)  # a clean launch leaves nothing to find
+    oracle.assert_close(d, want, "clean launch")
+    oracle.assert_close(run_gemm(handle, False, False, 128, 128, 128, 1.0, a, b, 1.0, c), want, "second clean launch")
+    _lib.check(L.b200_selftest_bounded_wait(handle._h, None, 1_000_000), "selftest")  # stands in for a launch whose wait ran out
+    _lib.check(L.b200_stream_sync(None), "sync")
+    with pytest.raises(B200Error) as e:
+        run_gemm(handle, False, False, 128, 128, 128, 1.0, a, b, 1.0, c)
+    assert e.value.status == _lib.DEVICE_TIMEOUT and "wait id 107" in str(e.value) and "enqueued nothing" in str(e.value)
+    oracle.assert_close(run_gemm(handle, False, False, 128, 128, 128, 1.0, a, b, 1.0, c), want, "call after the report")
+    handle.set_option(_lib.OPT_CHECK_ON_CALL, 0)
+    _lib.check(L.b200_selftest_bounded_wait(handle._h, None, 1_000_000), "selftest")
+    _lib.check(L.b200_stream_sync(None), "sync")
+    handle.gemm(False, False, 128, 128, 128, 1.0, CuArray(a), 128, CuArray(b), 128, 0.0, None, 128, CuArray(d), 128)  # silent
+    _lib.check(L.b200_stream_sync(None), "sync")
+    assert handle.device_status()[0] == 107
+
+
+def test_host_windows_that_end_with_their_buffer(handle, oracle):
+    """Operands with ld > rows only own ld * (cols - 1) + rows elements: windows cut from the bottom of a
+    taller host matrix (big[8:, :]) end exactly where the allocation ends.  The host-buffer entry point
+    must copy them window by window, never ld * cols elements."""
+    import ctypes as C
+
+    force(handle, _lib.KERNEL_AUTO)
+    M, N, K, pad = 256, 384, 128, 8
+    a, b, c = operands(M, N, K, False, False, seed=96)
+
+    def bottom_window(x):
+        """x as the last rows of a taller Fortran matrix held in a buffer with not one element to spare"""
+        rows, cols = x.shape
+        ld = rows + pad
+        flat = np.full(ld * (cols - 1) + rows + pad, np.nan, dtype=x.dtype)  # the view below starts `pad` elements in
+        view = np.lib.stride_tricks.as_strided(flat[pad:], shape=(rows, cols), strides=(x.itemsize, ld * x.itemsize))
+        view[...] = x
+        return flat, view, ld
+
+    fa, va, lda = bottom_window(a)
+    fb, vb, ldb = bottom_window(b)
+    fc, vc, ldc = bottom_window(c)
+    d = np.zeros((M, N), dtype=np.float32, order="F")
+    L = _lib.lib()
+    _lib.check(L.b200_gemm_f16f32_host(handle._h, 0, 0, M, N, K, 1.5, va.ctypes.data, lda, vb.ctypes.data, ldb, 0.5, vc.ctypes.data, ldc,
+                                       d.ctypes.data, M), "gemm_host")
+    assert fa.size == lda * (K - 1) + M + pad  # the buffers really end with their windows
+    oracle.assert_close(d, oracle.gemm_ref(False, False, 1.5, a, b, 0.5, c), "host windows")
+
+
 @pytest.mark.parametrize("tA,tB,N", [(True, False, 384), (False, True, 1300), (False, False, 2600)])
 def test_host_buffer_entry_point(handle, oracle, tA, tB, N):
     """b200_gemm_f16f32_host: host in, host out; wide N is cut into column slabs whose uploads,

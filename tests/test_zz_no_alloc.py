@@ -8,6 +8,8 @@ and status word) is a 16 MiB array inside the library image, shared by every cal
 the test makes two calls in a row with different problems and checks that neither sees the other's
 leftovers.  Collected last on purpose (file name): if it fails under ``-x`` every other test has
 already run."""
+import ctypes as C
+
 import numpy as np
 import pytest
 
@@ -65,3 +67,53 @@ def test_asynchronous_form_and_limits(lib, oracle):
     # argument checks
     assert static_gemm(lib, False, False, M, N, K, 1.0, a_dev, M, b_dev, K, 1.0, c_dev, d_dev, 1) == _lib.INVALID_ARG
     assert static_gemm(lib, False, False, M, N, K, 1.0, a_dev, M, b_dev, K, 1.0, None, d_dev, 2) == _lib.INVALID_ARG
+
+
+def test_status_accessor_reports_a_wait_that_ran_out(lib):
+    """The asynchronous form cannot return a time-out itself; b200_static_status is how such a caller
+    learns of one.  A warp that waits 1 ms on a barrier nothing signals makes the case (no fault, no
+    endless loop), the accessor reports it once and the word is clear afterwards."""
+    code, block, detail = C.c_int(-1), C.c_int(-1), C.c_int(-1)
+    _lib.check(lib.b200_static_status(C.byref(code), C.byref(block), C.byref(detail)), "static_status")
+    assert code.value == 0
+    _lib.check(lib.b200_static_selftest_bounded_wait(None, 1_000_000), "selftest")
+    _lib.check(lib.b200_stream_sync(None), "sync")
+    _lib.check(lib.b200_static_status(C.byref(code), C.byref(block), C.byref(detail)), "static_status")
+    assert (code.value, block.value) == (107, 0)
+    _lib.check(lib.b200_static_status(C.byref(code), C.byref(block), C.byref(detail)), "static_status")
+    assert code.value == 0
+    assert lib.b200_static_selftest_bounded_wait(None, 10) == _lib.INVALID_ARG
+    # a product through the same array right afterwards is unaffected
+    M, N, K = 256, 128, 512
+    a, b, c = operands(M, N, K, False, False, seed=204)
+    d_dev = CuHostArray(np.float32, shape=(M, N))
+    assert static_gemm(lib, False, False, M, N, K, 1.0, CuArray(a), M, CuArray(b), K, 0.0, None, d_dev, 2) == _lib.OK
+
+
+def test_no_device_memory_is_taken_after_the_warm_up(lib, oracle):
+    """What the entry point exists for: after b200_static_warmup (address lookup, kernel loading) calls of
+    any shape class leave the device's free memory exactly where it was -- no cudaMalloc, no growth of
+    a driver pool.  Two different problems, two calls each."""
+    import torch
+
+    torch.cuda.init()
+    _lib.check(lib.b200_static_warmup(), "static_warmup")
+    cases = [(False, False, 2048, 128, 2048, 4, 211), (True, False, 512, 512, 1024, 2, 212)]
+    staged = []
+    for (tA, tB, M, N, K, split_k, seed) in cases:
+        a, b, c = operands(M, N, K, tA, tB, seed=seed)
+        staged.append((tA, tB, M, N, K, split_k, a, b, c, CuArray(a), CuArray(b), CuArray(c), CuHostArray(np.float32, shape=(M, N))))
+    _lib.check(lib.b200_stream_sync(None), "sync")
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info(0)
+    for _ in range(2):
+        for (tA, tB, M, N, K, split_k, a, b, c, a_dev, b_dev, c_dev, d_dev) in staged:
+            assert static_gemm(lib, tA, tB, M, N, K, 1.0, a_dev, a.shape[0], b_dev, b.shape[0], 1.0, c_dev, d_dev, split_k, sync=0) == _lib.OK
+    _lib.check(lib.b200_stream_sync(None), "sync")
+    code = C.c_int(-1)
+    _lib.check(lib.b200_static_status(C.byref(code), None, None), "static_status")
+    assert code.value == 0
+    free_after, _ = torch.cuda.mem_get_info(0)
+    assert free_after == free_before, f"device free memory moved by {free_before - free_after} bytes across four calls"
+    for (tA, tB, M, N, K, split_k, a, b, c, a_dev, b_dev, c_dev, d_dev) in staged:
+        oracle.assert_close(Array(d_dev), oracle.gemm_ref(tA, tB, 1.0, a, b, 1.0, c), "after the memory check")
