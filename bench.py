@@ -611,9 +611,15 @@ def run_ours(args):
         del A, B, Cm, D
         torch.cuda.empty_cache()
         if not args.no_extras:
-            out["sustained"] = sustained_loop(h, stream, peaks, sampler)
+            # short legs first, each after a pause: the power-capped clock needs a moment to recover from
+            # the leg before it, and a leg that starts at the tail of another one's throttling measures that
+            time.sleep(1.0)
             out["skinny"] = skinny_leg(h, stream, peaks, sampler)
+            time.sleep(1.0)
             out["gemm4096"] = square_leg(h, stream, "gemm4096", peaks, sampler)
+            time.sleep(1.0)
+            out["sustained"] = sustained_loop(h, stream, peaks, sampler)
+            time.sleep(1.0)
         if not args.no_scaling_baseline:
             # The multi-GPU lines (N > 1) time the sharded 32768 x 32768 x 16384 product; its one-GPU time is measured
             # here so that the N-GPU values have a like-for-like denominator next to the headline 8192^3 number.

@@ -18,7 +18,7 @@ MATRIX_A, MATRIX_B, ACCUMULATOR = 0, 1, 2
 LOWER_WARP, LOWER_TCGEN05 = 0, 1
 KERNEL_AUTO, KERNEL_TCGEN05, KERNEL_SIMPLE = 0, 1, 2
 (OPT_FORCE_KERNEL, OPT_MAX_CTAS, OPT_WAIT_BUDGET_NS, OPT_TILE_N, OPT_SPLIT_K, OPT_CTA_PAIR,
- OPT_RASTER_GROUP, OPT_CHECK_ON_CALL) = range(8)
+ OPT_RASTER_GROUP, OPT_CHECK_ON_CALL, OPT_PDL) = range(9)
 SHARDED_GATED, SHARDED_NO_TRANSFER = 1, 2
 SHARDED_MAX_RANKS, SHARDED_MAX_PANELS, SHARDED_BLOB_BYTES = 64, 32, 128
 

@@ -88,6 +88,7 @@ GemmPlan make_plan(const b200_handle* h, const GemmProblem& g) {
     plan.max_ctas = h->max_ctas;
     plan.raster_group = h->raster_group;
     plan.wait_budget_ns = h->wait_budget_ns;
+    plan.pdl = h->pdl;
     int tile_n = h->tile_n;
     if (tile_n == 0) tile_n = g.N > 128 ? 256 : (g.N > 64 ? 128 : 64);
     int pair = h->cta_pair;
@@ -344,6 +345,10 @@ int b200_set_option(b200_handle* h, int option, int64_t value) {
             if (value != 0 && value != 1) return fail(B200_INVALID_ARG, "check_on_call must be 0 or 1");
             h->check_on_call = static_cast<int>(value);
             return B200_OK;
+        case B200_OPT_PDL:
+            if (value != 0 && value != 1) return fail(B200_INVALID_ARG, "pdl must be 0 or 1");
+            h->pdl = static_cast<int>(value);
+            return B200_OK;
         default:
             return fail(B200_INVALID_ARG, "unknown option");
     }
@@ -360,6 +365,7 @@ int b200_get_option(b200_handle* h, int option, int64_t* value) {
         case B200_OPT_CTA_PAIR: *value = h->cta_pair; return B200_OK;
         case B200_OPT_RASTER_GROUP: *value = h->raster_group; return B200_OK;
         case B200_OPT_CHECK_ON_CALL: *value = h->check_on_call; return B200_OK;
+        case B200_OPT_PDL: *value = h->pdl; return B200_OK;
         default: return fail(B200_INVALID_ARG, "unknown option");
     }
 }

@@ -155,6 +155,15 @@ int gemm_simple_launch(const GemmProblem& g, cudaStream_t stream, LaunchInfo* in
     return B200_OK;
 }
 
+int gemm_simple_preload() {
+    cudaFuncAttributes at;
+    B200_CUDA_TRY(cudaFuncGetAttributes(&at, gemm_simple_kernel<false, false>));
+    B200_CUDA_TRY(cudaFuncGetAttributes(&at, gemm_simple_kernel<false, true>));
+    B200_CUDA_TRY(cudaFuncGetAttributes(&at, gemm_simple_kernel<true, false>));
+    B200_CUDA_TRY(cudaFuncGetAttributes(&at, gemm_simple_kernel<true, true>));
+    return B200_OK;
+}
+
 }  // namespace b200
 
 extern "C" int b200_fill_f16(b200_stream stream, void* dptr, int64_t rows, int64_t cols, int64_t ld, uint64_t seed,

@@ -124,7 +124,7 @@ int opt_in_shared_memory() {
 
 template <int kBN, bool kAMn, bool kBMn, int kCtas, bool kBatch>
 int launch_kernel(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const CUtensorMap& tmD,
-                  const GemmParams& p, int grid, cudaStream_t stream) {
+                  const GemmParams& p, int grid, cudaStream_t stream, bool pdl) {
     using Cfg = GemmCfg<kBN, kAMn, kBMn, kCtas>;
     auto kern = gemm_f16f32_tcgen05<kBN, kAMn, kBMn, kCtas, kBatch>;
     if (int rc = opt_in_shared_memory<kBN, kAMn, kBMn, kCtas, kBatch>()) return rc;
@@ -142,27 +142,27 @@ int launch_kernel(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensor
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 2;
+    cfg.numAttrs = pdl ? 2 : 1;
     B200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmC, tmD, p));
     return B200_OK;
 }
 
 template <int kBN, bool kAMn, bool kBMn, int kCtas>
 int launch_one(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const CUtensorMap& tmD,
-               const GemmParams& p, int grid, cudaStream_t stream) {
-    if (p.batch > 1) return launch_kernel<kBN, kAMn, kBMn, kCtas, true>(tmA, tmB, tmC, tmD, p, grid, stream);
-    return launch_kernel<kBN, kAMn, kBMn, kCtas, false>(tmA, tmB, tmC, tmD, p, grid, stream);
+               const GemmParams& p, int grid, cudaStream_t stream, bool pdl) {
+    if (p.batch > 1) return launch_kernel<kBN, kAMn, kBMn, kCtas, true>(tmA, tmB, tmC, tmD, p, grid, stream, pdl);
+    return launch_kernel<kBN, kAMn, kBMn, kCtas, false>(tmA, tmB, tmC, tmD, p, grid, stream, pdl);
 }
 
 template <int kBN, int kCtas>
 int launch_layout(bool a_mn, bool b_mn, const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
-                  const CUtensorMap& tmD, const GemmParams& p, int grid, cudaStream_t stream) {
+                  const CUtensorMap& tmD, const GemmParams& p, int grid, cudaStream_t stream, bool pdl) {
     if (a_mn) {
-        if (b_mn) return launch_one<kBN, true, true, kCtas>(tmA, tmB, tmC, tmD, p, grid, stream);
-        return launch_one<kBN, true, false, kCtas>(tmA, tmB, tmC, tmD, p, grid, stream);
+        if (b_mn) return launch_one<kBN, true, true, kCtas>(tmA, tmB, tmC, tmD, p, grid, stream, pdl);
+        return launch_one<kBN, true, false, kCtas>(tmA, tmB, tmC, tmD, p, grid, stream, pdl);
     }
-    if (b_mn) return launch_one<kBN, false, true, kCtas>(tmA, tmB, tmC, tmD, p, grid, stream);
-    return launch_one<kBN, false, false, kCtas>(tmA, tmB, tmC, tmD, p, grid, stream);
+    if (b_mn) return launch_one<kBN, false, true, kCtas>(tmA, tmB, tmC, tmD, p, grid, stream, pdl);
+    return launch_one<kBN, false, false, kCtas>(tmA, tmB, tmC, tmD, p, grid, stream, pdl);
 }
 
 inline int64_t round_up(int64_t x, int64_t m) { return (x + m - 1) / m * m; }
@@ -359,13 +359,13 @@ int gemm_tcgen05_launch(const GemmProblem& g, const GemmPlan& plan, float* scrat
     }
 
     if (plan.cta_pair == 2) {
-        if (plan.tile_n == 256) rc = launch_layout<256, 2>(a_mn, b_mn, tmA, tmB, tmC, tmD, p, grid, stream);
-        else if (plan.tile_n == 128) rc = launch_layout<128, 2>(a_mn, b_mn, tmA, tmB, tmC, tmD, p, grid, stream);
+        if (plan.tile_n == 256) rc = launch_layout<256, 2>(a_mn, b_mn, tmA, tmB, tmC, tmD, p, grid, stream, plan.pdl != 0);
+        else if (plan.tile_n == 128) rc = launch_layout<128, 2>(a_mn, b_mn, tmA, tmB, tmC, tmD, p, grid, stream, plan.pdl != 0);
         else return fail(B200_UNSUPPORTED, "2-CTA tiles exist for tile_n 128 and 256");
     } else {
-        if (plan.tile_n == 256) rc = launch_layout<256, 1>(a_mn, b_mn, tmA, tmB, tmC, tmD, p, grid, stream);
-        else if (plan.tile_n == 128) rc = launch_layout<128, 1>(a_mn, b_mn, tmA, tmB, tmC, tmD, p, grid, stream);
-        else if (plan.tile_n == 64) rc = launch_layout<64, 1>(a_mn, b_mn, tmA, tmB, tmC, tmD, p, grid, stream);
+        if (plan.tile_n == 256) rc = launch_layout<256, 1>(a_mn, b_mn, tmA, tmB, tmC, tmD, p, grid, stream, plan.pdl != 0);
+        else if (plan.tile_n == 128) rc = launch_layout<128, 1>(a_mn, b_mn, tmA, tmB, tmC, tmD, p, grid, stream, plan.pdl != 0);
+        else if (plan.tile_n == 64) rc = launch_layout<64, 1>(a_mn, b_mn, tmA, tmB, tmC, tmD, p, grid, stream, plan.pdl != 0);
         else return fail(B200_UNSUPPORTED, "tile_n must be 64, 128 or 256");
     }
     if (rc) return rc;

@@ -61,6 +61,7 @@ struct GemmPlan {
     int max_ctas;  // grid cap (0 = SM count)
     int raster_group;  // 0 = default
     unsigned long long wait_budget_ns;
+    int pdl = 1;       // launch with programmatic stream serialization
 };
 
 struct LaunchInfo {
@@ -83,6 +84,7 @@ struct b200_handle {
     int cta_pair = 0;
     int raster_group = 0;
     int check_on_call = 0;
+    int pdl = 1;
     // workspace of the host-buffer entry point and split-K scratch (grown on demand)
     void* ws[4] = {nullptr, nullptr, nullptr, nullptr};
     size_t ws_bytes[4] = {0, 0, 0, 0};
@@ -122,6 +124,9 @@ int gemm_tcgen05_launch(const GemmProblem& g, const GemmPlan& plan, float* scrat
 // Loads every non-batched instantiation of the tcgen05 kernel and the split-K reduction on the current
 // device and opts them in to their shared memory, so that no later launch does it.
 int gemm_tcgen05_preload();
+
+// Makes the driver load the plain kernel's four layout variants on the current device.
+int gemm_simple_preload();
 
 // Enqueue the plain shared-memory kernel: any shape, any alignment.
 int gemm_simple_launch(const GemmProblem& g, cudaStream_t stream, LaunchInfo* info);

@@ -332,6 +332,11 @@ int b200_sharded_create(b200_sharded** out, b200_handle* h, int rank, int world,
         b200_sharded_destroy(s);
         return code;
     };
+    // The driver loads a kernel when it is first launched, and loading may wait for everything the
+    // context has in flight.  A product enqueues stream-level waits for peers BEFORE its first launch:
+    // a first launch that had to load its kernel would then wait for the peers on the host -- for good
+    // when the peers are ranks of this very thread.  So every kernel a product can launch is loaded here.
+    if ((rc = gemm_tcgen05_preload()) || (rc = gemm_simple_preload())) return bail(rc);
     cudaError_t e;
     if ((e = cudaMalloc(&s->a_local, static_cast<size_t>(2) * M * K)) != cudaSuccess) return bail(cuda_fail(e, "sharded_create: A"));
     s->a_peers.assign(world, nullptr);
@@ -507,13 +512,19 @@ int b200_sharded_wait(b200_sharded* s, int64_t timeout_ms) {
     const auto t0 = std::chrono::steady_clock::now();
     // host-side poll, bounded by the caller's deadline
     bool expired = false, busy = true;
+    unsigned busy_mask = 0;
     while (busy && !expired) {
         busy = false;
+        busy_mask = 0;
         for (int i = 0; i < n_streams; ++i) {
             if (i > 0 && !streams[i]) continue;
             cudaError_t e = cudaStreamQuery(streams[i]);
-            if (e == cudaErrorNotReady) busy = true;
-            else if (e != cudaSuccess) return cuda_fail(e, "sharded_wait: cudaStreamQuery");
+            if (e == cudaErrorNotReady) {
+                busy = true;
+                busy_mask |= 1u << i;
+            } else if (e != cudaSuccess) {
+                return cuda_fail(e, "sharded_wait: cudaStreamQuery");
+            }
         }
         if (!busy) break;
         const auto ms = std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count();
@@ -535,6 +546,21 @@ int b200_sharded_wait(b200_sharded* s, int64_t timeout_ms) {
         }
         if (!set32) return fail(B200_CUDA_ERROR, "cuMemsetD32Async entry point not found");
         if (!s->rescue) B200_CUDA_TRY(cudaStreamCreateWithFlags(&s->rescue, cudaStreamNonBlocking));
+        // what this rank has heard so far, for the error text: which peers said "done", how many panels arrived
+        std::vector<uint32_t> seen(B200_SHARDED_FLAG_BYTES / 4, 0);
+        std::string heard;
+        if (cudaMemcpyAsync(seen.data(), s->flags_local, B200_SHARDED_FLAG_BYTES, cudaMemcpyDeviceToHost, s->rescue) == cudaSuccess &&
+            cudaStreamSynchronize(s->rescue) == cudaSuccess) {
+            heard = "; silent peers:";
+            for (int g = 0; g < s->world; ++g)
+                if (g != s->rank && seen[word_done(g) / 4] < s->epoch) heard += " " + std::to_string(g);
+            int scat = 0;
+            for (int p = 0; p < s->lay.panels(); ++p) scat += seen[word_scat(p) / 4] >= s->epoch;
+            heard += "; panels scattered to this rank: " + std::to_string(scat) + " of " + std::to_string(s->lay.panels());
+        }
+        cudaGetLastError();
+        heard += std::string("; streams still busy:") + ((busy_mask & 1u) ? " compute" : "") + ((busy_mask & 2u) ? " scatter" : "") +
+                 ((busy_mask & 4u) ? " gather" : "");
         CUresult r = set32(reinterpret_cast<CUdeviceptr>(s->flags_local), s->epoch, B200_SHARDED_FLAG_BYTES / 4, s->rescue);
         if (r != CUDA_SUCCESS) return fail(B200_CUDA_ERROR, "cuMemsetD32Async failed (CUresult " + std::to_string(static_cast<int>(r)) + ")");
         // the gated form also polls gate words from inside the kernel (bounded there); open them too
@@ -547,7 +573,7 @@ int b200_sharded_wait(b200_sharded* s, int64_t timeout_ms) {
         read_status(s->h, word);
         s->in_flight = false;
         return fail(B200_PEER_TIMEOUT, "sharded_wait: no word from a peer within " + std::to_string(timeout_ms) +
-                                           " ms (epoch " + std::to_string(s->epoch) + "); the waits were released, D is not valid");
+                                           " ms (epoch " + std::to_string(s->epoch) + ")" + heard + "; the waits were released, D is not valid");
     }
     s->in_flight = false;
     int word[4] = {0, 0, 0, 0};

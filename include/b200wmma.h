@@ -66,6 +66,9 @@ enum {
     B200_OPT_SPLIT_K = 4,        /* 0 = auto, 1 = off, n>1 = split the K loop n ways              */
     B200_OPT_CTA_PAIR = 5,       /* 0 = auto, 1 = one-CTA tiles only, 2 = force 2-CTA tiles       */
     B200_OPT_RASTER_GROUP = 6,   /* tile rows per rasterisation group (0 = default)               */
+    B200_OPT_PDL = 8,            /* 1 (default) = tcgen05 GEMM kernels are launched with programmatic   */
+                                 /* stream serialization: their set-up overlaps the tail of the kernel  */
+                                 /* before them in the stream; 0 = ordinary launches                    */
     B200_OPT_CHECK_ON_CALL = 7   /* 1 = every GEMM entry point first looks at the status word of the  */
                                  /* handle's previous launch, if that launch has finished, and returns */
                                  /* B200_DEVICE_TIMEOUT when a wait ran out in it: the reference polls */

@@ -10,6 +10,7 @@ single-launch form polls from inside a kernel and is therefore not run here).
     sharded_local_worker.py timeout                              a peer that never calls: deadline, error, context alive
 """
 import ctypes as C
+import os
 import sys
 from pathlib import Path
 
@@ -51,6 +52,8 @@ def make_ranks(world, M, N, K, panels):
     handles = [Handle(0) for _ in range(world)]
     for h in handles:
         h.set_option(_lib.OPT_WAIT_BUDGET_NS, 500_000_000)
+        if os.environ.get("B200_TEST_PDL") is not None:
+            h.set_option(_lib.OPT_PDL, int(os.environ["B200_TEST_PDL"]))
     objs = [ShardedGemm(handles[r], M, N, K, rank=r, world=world, panels=panels) for r in range(world)]
     for o in objs:
         o.attach_local(objs)
@@ -77,8 +80,10 @@ def run(world, M, N, K, panels):
         for r, o in enumerate(objs):
             b, c, b_dev, c_dev, d_dev = slabs[r]
             o.run(alpha, b_dev.ptr if b_dev else 0, beta, c_dev.ptr if c_dev else 0, d_dev.ptr, stream=streams[r])
-        for o in objs:
-            o.wait(20000)
+            print(f"product {rep}: rank {r} enqueued", flush=True)
+        for r, o in enumerate(objs):
+            o.wait(10000)
+            print(f"product {rep}: rank {r} finished", flush=True)
     for r, o in enumerate(objs):
         if r:
             got = download(o.a_ptr, (M, K), np.float16)
