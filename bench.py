@@ -397,6 +397,10 @@ def run_ours(args):
             dist.all_gather_object(blobs, blob)
             return blobs
         sg = ShardedGemm(h, M, N, K, rank=rank, world=world, panels=args.panels, exchange=exchange if world > 1 else None)
+        if world > 1:
+            sg.set_option(_lib.SHARDED_OPT_SCATTER_LANES, args.scatter_lanes)
+            sg.set_option(_lib.SHARDED_OPT_GATHER_LANES, args.gather_lanes)
+            sg.set_option(_lib.SHARDED_OPT_FIRST_GROUP, args.first_group)
         n0, ns = sg.n0, sg.slab_cols
         A = torch.as_tensor(sg.a_view(), device=torch.device("cuda", local_rank))
         n_launches = 1 if args.gated else sg.n_groups
@@ -422,9 +426,9 @@ def run_ours(args):
     if Cm is not None:
         rng.fill_device(Cm.data_ptr(), M, ns, M, w["seed"], 2, dist_code(rng, w["c_dist"]), 1.0, False, stream, col0=n0)
 
-    def step(no_transfer=False):
+    def step(no_transfer=False, no_compute=False):
         if sharded and p2p:
-            sg.run(w["alpha"], B, w["beta"], Cm, D, stream=stream, gated=args.gated, no_transfer=no_transfer)
+            sg.run(w["alpha"], B, w["beta"], Cm, D, stream=stream, gated=args.gated, no_transfer=no_transfer, no_compute=no_compute)
         elif sharded:
             sg.run(w["alpha"], A, B, w["beta"], Cm, D)
         else:
@@ -469,7 +473,7 @@ def run_ours(args):
 
     # ---- sharded runs: the result proves itself, and the exposed transfer becomes a number -------------
     parity = None
-    compute_only_ms = None
+    compute_only_ms = transfer_only_ms = None
     if sharded:
         mine = check_slab_tiles(w, D, n0, ns, A=A if rank != 0 else None)
         if dist is not None:
@@ -493,10 +497,22 @@ def run_ours(args):
             ms, _ = event_timed(torch, lambda: step(no_transfer=True), k, 2)
             compute_only_ms = max_over_ranks(ms / k)
             barrier()
+            # and the transfer alone (every copy, flag and wait, no launch): the floor the links set
+            ms, _ = event_timed(torch, lambda: step(no_compute=True), k, 2)
+            sg.wait(60000)
+            transfer_only_ms = max_over_ranks(ms / k)
+            barrier()
 
     # ---- end to end through the host-buffer API -------------------------------------------
     e2e_steps = max(1, min(args.steps, args.e2e_steps))
-    if sharded:
+    if args.no_e2e:
+        e2e_steps = 0
+    if sharded and args.no_e2e:
+        h2d = d2h = 0
+
+        def e2e_step():
+            pass
+    elif sharded:
         hA = torch.empty(M * K, dtype=torch.float16).pin_memory() if rank == 0 else None
         hB = torch.empty(K * max(ns, 1), dtype=torch.float16).pin_memory()
         hC = torch.empty(M * max(ns, 1), dtype=torch.float32).pin_memory()
@@ -549,8 +565,8 @@ def run_ours(args):
     for _ in range(e2e_steps):
         e2e_step()
     barrier()
-    e2e_s = max_over_ranks((time.perf_counter() - t0) / e2e_steps)
-    e2e_tflops = flops / e2e_s / 1e12
+    e2e_s = max_over_ranks((time.perf_counter() - t0) / max(e2e_steps, 1))
+    e2e_tflops = flops / e2e_s / 1e12 if e2e_steps else 0.0
     if sharded and p2p:
         barrier()
         sg.close()
@@ -605,6 +621,8 @@ def run_ours(args):
     if compute_only_ms is not None:
         out["compute_only_ms"] = round(compute_only_ms, 4)
         out["exposed_transfer_ms"] = round(ms_step - compute_only_ms, 4)
+    if transfer_only_ms is not None:
+        out["transfer_only_ms"] = round(transfer_only_ms, 4)
     if world == 1 and args.workload is None:
         # the other single-GPU configurations, each timed on its own: they share the line so that one
         # default run records every headline figure
@@ -908,8 +926,12 @@ def main():
     ap.add_argument("--nccl-ctas", type=int, default=8, help="SMs left to NCCL while a broadcast is in flight (transport nccl)")
     ap.add_argument("--gated", action="store_true", help="p2p transport: one gated GEMM launch instead of a few launches over growing K ranges")
     ap.add_argument("--transport", default="p2p", choices=["p2p", "nccl"], help="how A reaches the other ranks (sharded)")
+    ap.add_argument("--scatter-lanes", type=int, default=1, help="streams rank 0 spreads its copies over (sharded, p2p)")
+    ap.add_argument("--gather-lanes", type=int, default=1, help="streams the other ranks spread their forwarding copies over (sharded, p2p)")
+    ap.add_argument("--first-group", type=int, default=1, help="panels in the first GEMM launch (sharded, p2p)")
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-e2e", action="store_true", help="sharded runs: skip the end-to-end leg (experiments; the line then has e2e.value 0)")
     ap.add_argument("--no-scaling-baseline", action="store_true", help="N=1: skip the one-GPU run of the sharded workload")
     ap.add_argument("--no-extras", action="store_true", help="N=1: skip the sustained / skinny / gemm4096 legs")
     args = ap.parse_args()

@@ -19,7 +19,8 @@ LOWER_WARP, LOWER_TCGEN05 = 0, 1
 KERNEL_AUTO, KERNEL_TCGEN05, KERNEL_SIMPLE = 0, 1, 2
 (OPT_FORCE_KERNEL, OPT_MAX_CTAS, OPT_WAIT_BUDGET_NS, OPT_TILE_N, OPT_SPLIT_K, OPT_CTA_PAIR,
  OPT_RASTER_GROUP, OPT_CHECK_ON_CALL, OPT_PDL) = range(9)
-SHARDED_GATED, SHARDED_NO_TRANSFER = 1, 2
+SHARDED_GATED, SHARDED_NO_TRANSFER, SHARDED_NO_COMPUTE = 1, 2, 4
+SHARDED_OPT_SCATTER_LANES, SHARDED_OPT_GATHER_LANES, SHARDED_OPT_FIRST_GROUP = 0, 1, 2
 SHARDED_MAX_RANKS, SHARDED_MAX_PANELS, SHARDED_BLOB_BYTES = 64, 32, 128
 
 _i, _i64, _u64, _f, _p, _sz = C.c_int, C.c_int64, C.c_uint64, C.c_float, C.c_void_p, C.c_size_t
@@ -66,6 +67,7 @@ SIGNATURES = {
     "b200_static_selftest_bounded_wait": (_i, [_p, _i64]),
     "b200_sharded_create": (_i, [_pp, _p, _i, _i, _i64, _i64, _i64, _i]),
     "b200_sharded_destroy": (_i, [_p]),
+    "b200_sharded_set_option": (_i, [_p, _i, _i64]),
     "b200_sharded_info": (_i, [_p, C.POINTER(_i64), C.POINTER(_i64), _pp, _pp, _ip, _ip]),
     "b200_sharded_ipc_blob": (_i, [_p, _p]),
     "b200_sharded_attach": (_i, [_p, _p]),

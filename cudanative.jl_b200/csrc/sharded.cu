@@ -192,6 +192,11 @@ struct b200_sharded {
     std::vector<char> ipc_mapped;  // peer g was opened through CUDA IPC (needs closing)
     bool attached = false;
     cudaStream_t scatter = nullptr, gather = nullptr, rescue = nullptr;
+    // Copies to different receivers may run side by side on several copy engines: lane 0 of each kind is
+    // the stream above, further lanes are created when the option asks for them.
+    std::vector<cudaStream_t> scatter_lanes, gather_lanes;
+    int first_group = 1;
+    int panels_requested = 16;
     cudaEvent_t fork = nullptr;
     uint32_t* gate_words = nullptr;
     uint32_t epoch = 0;
@@ -210,13 +215,17 @@ int p2p_begin(b200_sharded* s, cudaStream_t compute) {
     for (int g = 0; g < s->world; ++g)
         if (g != s->rank) tell.write(s->flag_peers[g], word_done(s->rank), s->epoch);
     if ((rc = tell.flush(compute, "done flags"))) return rc;
-    for (int which = 0; which < 2; ++which) {
-        if (which == 0 && s->rank != 0) continue;  // only rank 0 scatters
+    auto hear_on = [&](cudaStream_t st) -> int {
         MemOps hear;
         for (int g = 0; g < s->world; ++g)
             if (g != s->rank) hear.wait(s->flags_local, word_done(g), s->epoch);
-        if ((rc = hear.flush(which == 0 ? s->scatter : s->gather, "done waits"))) return rc;
-    }
+        return hear.flush(st, "done waits");
+    };
+    if (s->rank == 0)  // only rank 0 scatters
+        for (cudaStream_t st : s->scatter_lanes)
+            if ((rc = hear_on(st))) return rc;
+    for (cudaStream_t st : s->gather_lanes)
+        if ((rc = hear_on(st))) return rc;
     return B200_OK;
 }
 
@@ -224,40 +233,39 @@ int p2p_exchange(b200_sharded* s, int p0, int p1, cudaStream_t compute, bool gat
     const int rank = s->rank, world = s->world;
     const int64_t M = s->M;
     int rc;
-    auto copy_cols = [&](int dst, int64_t c0, int64_t c1, cudaStream_t st) -> int {
-        if (c1 <= c0) return B200_OK;
-        char* d = static_cast<char*>(s->a_peers[dst]) + 2 * c0 * M;
-        const char* src = static_cast<const char*>(s->a_local) + 2 * c0 * M;
-        B200_CUDA_TRY(cudaMemcpyAsync(d, src, static_cast<size_t>(2 * (c1 - c0) * M), cudaMemcpyDefault, st));
-        return B200_OK;
+    // one copy and, right behind it on the same stream, the word that tells the receiver it has landed
+    auto send_cols = [&](int dst, int64_t c0, int64_t c1, cudaStream_t st, size_t flag_word) -> int {
+        if (c1 > c0) {
+            char* d = static_cast<char*>(s->a_peers[dst]) + 2 * c0 * M;
+            const char* src = static_cast<const char*>(s->a_local) + 2 * c0 * M;
+            B200_CUDA_TRY(cudaMemcpyAsync(d, src, static_cast<size_t>(2 * (c1 - c0) * M), cudaMemcpyDefault, st));
+        }
+        MemOps done;
+        done.write(s->flag_peers[dst], flag_word, s->epoch);
+        return done.flush(st, "arrival flag");
     };
+    const int ns = static_cast<int>(s->scatter_lanes.size()), ng = static_cast<int>(s->gather_lanes.size());
     for (int p = p0; p < p1; ++p) {
         const int64_t* sub = s->lay.sub.data() + static_cast<size_t>(p) * world * 2;
         if (rank == 0) {  // scatter: sub-block g goes to rank g
-            MemOps done;
-            for (int g = 1; g < world; ++g) {
-                if ((rc = copy_cols(g, sub[2 * g], sub[2 * g + 1], s->scatter))) return rc;
-                done.write(s->flag_peers[g], word_scat(p), s->epoch);
+            for (int g = 1; g < world; ++g)
+                if ((rc = send_cols(g, sub[2 * g], sub[2 * g + 1], s->scatter_lanes[(g - 1) % ns], word_scat(p)))) return rc;
+        } else {
+            // all-gather: my sub-block goes to everybody but rank 0, which has all of A.  It must be here
+            // before I can pass it on.  Destinations are visited starting after this rank, so that at any
+            // moment the senders aim at different receivers instead of all at the same one.
+            for (int l = 0; l < std::min(ng, world - 2); ++l) {
+                MemOps got;
+                got.wait(s->flags_local, word_scat(p), s->epoch);
+                if ((rc = got.flush(s->gather_lanes[l], "scatter wait"))) return rc;
             }
-            if ((rc = done.flush(s->scatter, "scatter flags"))) return rc;
-        } else {          // my sub-block must be here before I can pass it on
-            MemOps got;
-            got.wait(s->flags_local, word_scat(p), s->epoch);
-            if ((rc = got.flush(s->gather, "scatter wait"))) return rc;
-        }
-        {   // all-gather: my sub-block goes to everybody but rank 0, which has all of A
-            MemOps done;
-            // destinations are visited starting after this rank, so that at any moment the senders
-            // aim at different receivers instead of all at the same one
+            int n_sent = 0;
             for (int i = 1; i < world; ++i) {
                 const int dst = (rank + i) % world;
-                if (dst == 0 || rank == 0) continue;
-                if ((rc = copy_cols(dst, sub[2 * rank], sub[2 * rank + 1], s->gather))) return rc;
-                done.write(s->flag_peers[dst], word_gath(p, rank), s->epoch);
+                if (dst == 0) continue;
+                if ((rc = send_cols(dst, sub[2 * rank], sub[2 * rank + 1], s->gather_lanes[n_sent % ng], word_gath(p, rank)))) return rc;
+                ++n_sent;
             }
-            if ((rc = done.flush(s->gather, "all-gather flags"))) return rc;
-        }
-        if (rank != 0) {
             // arrival of panel p on this rank: my own sub-block (scatter) and everybody else's
             MemOps here;
             here.wait(s->flags_local, word_scat(p), s->epoch);
@@ -324,6 +332,7 @@ int b200_sharded_create(b200_sharded** out, b200_handle* h, int rank, int world,
     s->M = M;
     s->N = N;
     s->K = K;
+    s->panels_requested = panels;
     if ((rc = make_layout(world, N, K, panels, 1, &s->lay))) {
         delete s;
         return rc;
@@ -354,6 +363,8 @@ int b200_sharded_create(b200_sharded** out, b200_handle* h, int rank, int world,
         s->flag_peers[rank] = s->flags_local;
         if ((e = cudaStreamCreateWithFlags(&s->scatter, cudaStreamNonBlocking)) != cudaSuccess) return bail(cuda_fail(e, "sharded_create: stream"));
         if ((e = cudaStreamCreateWithFlags(&s->gather, cudaStreamNonBlocking)) != cudaSuccess) return bail(cuda_fail(e, "sharded_create: stream"));
+        s->scatter_lanes.assign(1, s->scatter);
+        s->gather_lanes.assign(1, s->gather);
         if ((e = cudaEventCreateWithFlags(&s->fork, cudaEventDisableTiming)) != cudaSuccess) return bail(cuda_fail(e, "sharded_create: event"));
     } else {
         s->attached = true;
@@ -370,6 +381,8 @@ int b200_sharded_destroy(b200_sharded* s) {
         if (s->a_peers[g]) cudaIpcCloseMemHandle(s->a_peers[g]);
         if (s->flag_peers[g]) cudaIpcCloseMemHandle(s->flag_peers[g]);
     }
+    for (size_t i = 1; i < s->scatter_lanes.size(); ++i) cudaStreamDestroy(s->scatter_lanes[i]);
+    for (size_t i = 1; i < s->gather_lanes.size(); ++i) cudaStreamDestroy(s->gather_lanes[i]);
     if (s->scatter) cudaStreamDestroy(s->scatter);
     if (s->gather) cudaStreamDestroy(s->gather);
     if (s->rescue) cudaStreamDestroy(s->rescue);
@@ -446,12 +459,13 @@ int b200_sharded_run(b200_sharded* s, b200_stream stream, float alpha, const voi
     if (!s->attached) return fail(B200_INVALID_ARG, "sharded_run: peers are not attached yet (b200_sharded_attach)");
     if (s->poisoned)
         return fail(B200_PEER_TIMEOUT, "sharded_run: an earlier product timed out waiting for a peer; destroy the object on every rank");
-    if (flags & ~(B200_SHARDED_GATED | B200_SHARDED_NO_TRANSFER)) return fail(B200_INVALID_ARG, "sharded_run: unknown flag");
+    if (flags & ~(B200_SHARDED_GATED | B200_SHARDED_NO_TRANSFER | B200_SHARDED_NO_COMPUTE)) return fail(B200_INVALID_ARG, "sharded_run: unknown flag");
     int rc;
     if ((rc = check_current_device(s->h))) return rc;
     b200_handle* h = s->h;
     cudaStream_t cs = static_cast<cudaStream_t>(stream);
-    const int64_t ns = s->lay.slab[s->rank + 1] - s->lay.slab[s->rank];
+    // transfer only: the slab is treated as empty, the copies, flags and waits are all there
+    const int64_t ns = (flags & B200_SHARDED_NO_COMPUTE) ? 0 : s->lay.slab[s->rank + 1] - s->lay.slab[s->rank];
     const int64_t M = s->M, K = s->K;
     const bool transfer = s->world > 1 && !(flags & B200_SHARDED_NO_TRANSFER);
     const bool gated = transfer && (flags & B200_SHARDED_GATED);
@@ -461,8 +475,8 @@ int b200_sharded_run(b200_sharded* s, b200_stream stream, float alpha, const voi
     if (transfer) {
         // the transfer streams start behind whatever the caller enqueued before this call (rank 0's A)
         B200_CUDA_TRY(cudaEventRecord(s->fork, cs));
-        B200_CUDA_TRY(cudaStreamWaitEvent(s->scatter, s->fork, 0));
-        B200_CUDA_TRY(cudaStreamWaitEvent(s->gather, s->fork, 0));
+        for (cudaStream_t st : s->scatter_lanes) B200_CUDA_TRY(cudaStreamWaitEvent(st, s->fork, 0));
+        for (cudaStream_t st : s->gather_lanes) B200_CUDA_TRY(cudaStreamWaitEvent(st, s->fork, 0));
         ++s->epoch;
         if ((rc = p2p_begin(s, cs))) return rc;
         s->last_compute = cs;
@@ -501,14 +515,56 @@ int b200_sharded_run(b200_sharded* s, b200_stream stream, float alpha, const voi
     return B200_OK;
 }
 
+int b200_sharded_set_option(b200_sharded* s, int option, int64_t value) {
+    if (!s) return fail(B200_INVALID_ARG, "sharded_set_option: null object");
+    if (s->in_flight) return fail(B200_INVALID_ARG, "sharded_set_option: a product is in flight (b200_sharded_wait first)");
+    int rc;
+    if ((rc = check_current_device(s->h))) return rc;
+    auto grow = [&](std::vector<cudaStream_t>& lanes, int64_t n) -> int {
+        if (s->world == 1) return B200_OK;
+        while (static_cast<int64_t>(lanes.size()) < n) {
+            cudaStream_t st = nullptr;
+            B200_CUDA_TRY(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
+            lanes.push_back(st);
+        }
+        while (static_cast<int64_t>(lanes.size()) > n) {
+            B200_CUDA_TRY(cudaStreamDestroy(lanes.back()));
+            lanes.pop_back();
+        }
+        return B200_OK;
+    };
+    switch (option) {
+        case B200_SHARDED_OPT_SCATTER_LANES:
+            if (value < 1 || value > 8) return fail(B200_INVALID_ARG, "scatter lanes must be in [1, 8]");
+            return grow(s->scatter_lanes, value);
+        case B200_SHARDED_OPT_GATHER_LANES:
+            if (value < 1 || value > 8) return fail(B200_INVALID_ARG, "gather lanes must be in [1, 8]");
+            return grow(s->gather_lanes, value);
+        case B200_SHARDED_OPT_FIRST_GROUP: {
+            if (value < 1 || value > B200_SHARDED_MAX_PANELS) return fail(B200_INVALID_ARG, "first group must be in [1, 32] panels");
+            ShardLayout L;
+            if ((rc = make_layout(s->world, s->N, s->K, s->panels_requested, static_cast<int>(value), &L))) return rc;
+            if (L.panels() != s->lay.panels()) return fail(B200_INVALID_ARG, "sharded_set_option: layout changed");
+            s->lay.group = L.group;
+            s->first_group = static_cast<int>(value);
+            return B200_OK;
+        }
+        default:
+            return fail(B200_INVALID_ARG, "sharded_set_option: unknown option");
+    }
+}
+
 int b200_sharded_wait(b200_sharded* s, int64_t timeout_ms) {
     if (!s) return fail(B200_INVALID_ARG, "sharded_wait: null object");
     if (timeout_ms < 1) return fail(B200_INVALID_ARG, "sharded_wait: the timeout must be at least 1 ms");
     int rc;
     if ((rc = check_current_device(s->h))) return rc;
     if (s->poisoned) return fail(B200_PEER_TIMEOUT, "sharded_wait: an earlier product timed out waiting for a peer");
-    cudaStream_t streams[3] = {s->last_compute, s->scatter, s->gather};
-    const int n_streams = s->world > 1 ? 3 : 1;
+    // (stream, kind): kind 0 = the caller's stream of the last product, 1 = scatter lane, 2 = gather lane
+    std::vector<std::pair<cudaStream_t, int>> streams;
+    streams.emplace_back(s->last_compute, 0);
+    for (cudaStream_t st : s->scatter_lanes) streams.emplace_back(st, 1);
+    for (cudaStream_t st : s->gather_lanes) streams.emplace_back(st, 2);
     const auto t0 = std::chrono::steady_clock::now();
     // host-side poll, bounded by the caller's deadline
     bool expired = false, busy = true;
@@ -516,12 +572,11 @@ int b200_sharded_wait(b200_sharded* s, int64_t timeout_ms) {
     while (busy && !expired) {
         busy = false;
         busy_mask = 0;
-        for (int i = 0; i < n_streams; ++i) {
-            if (i > 0 && !streams[i]) continue;
-            cudaError_t e = cudaStreamQuery(streams[i]);
+        for (const auto& sk : streams) {
+            cudaError_t e = cudaStreamQuery(sk.first);
             if (e == cudaErrorNotReady) {
                 busy = true;
-                busy_mask |= 1u << i;
+                busy_mask |= 1u << sk.second;
             } else if (e != cudaSuccess) {
                 return cuda_fail(e, "sharded_wait: cudaStreamQuery");
             }
@@ -567,8 +622,7 @@ int b200_sharded_wait(b200_sharded* s, int64_t timeout_ms) {
         B200_CUDA_TRY(cudaMemsetAsync(s->gate_words, 1, 4 * B200_SHARDED_MAX_PANELS, s->rescue));
         B200_CUDA_TRY(cudaStreamSynchronize(s->rescue));
         // the released work is finite (copies and GEMM launches with bounded waits): let it drain
-        for (int i = 0; i < n_streams; ++i)
-            if (i == 0 || streams[i]) B200_CUDA_TRY(cudaStreamSynchronize(streams[i]));
+        for (const auto& sk : streams) B200_CUDA_TRY(cudaStreamSynchronize(sk.first));
         int word[4];
         read_status(s->h, word);
         s->in_flight = false;

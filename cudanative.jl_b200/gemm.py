@@ -287,12 +287,20 @@ class ShardedGemm:
         f = (C.c_void_p * self.world)(*[p.flags_ptr for p in peers])
         _lib.check(_lib.lib().b200_sharded_attach_local(self._s, a, f), "sharded_attach_local")
 
+    def set_option(self, option: int, value: int) -> None:
+        """One of _lib.SHARDED_OPT_* (b200_sharded_set_option); the same on every rank, between products."""
+        _lib.check(_lib.lib().b200_sharded_set_option(self._s, option, int(value)), "sharded_set_option")
+        n_p, n_g = C.c_int(), C.c_int()
+        _lib.check(_lib.lib().b200_sharded_info(self._s, None, None, None, None, C.byref(n_p), C.byref(n_g)), "sharded_info")
+        self.n_panels, self.n_groups = n_p.value, n_g.value
+
     def run(self, alpha: float, B_slab, beta: float, C_slab, D_slab, *, stream=None, gated: bool = False,
-            no_transfer: bool = False, ldb: int | None = None, ldc: int | None = None, ldd: int | None = None) -> None:
+            no_transfer: bool = False, no_compute: bool = False, ldb: int | None = None, ldc: int | None = None, ldd: int | None = None) -> None:
         """Enqueue one product (b200_sharded_run).  B_slab: K x slab_cols, C_slab / D_slab: M x
         slab_cols, column-major device matrices (addresses, DevicePtr, CuHostArray or CUDA tensors).
         Every rank must make the call, also one whose slab is empty."""
-        flags = (_lib.SHARDED_GATED if gated else 0) | (_lib.SHARDED_NO_TRANSFER if no_transfer else 0)
+        flags = ((_lib.SHARDED_GATED if gated else 0) | (_lib.SHARDED_NO_TRANSFER if no_transfer else 0) |
+                 (_lib.SHARDED_NO_COMPUTE if no_compute else 0))
         _lib.check(_lib.lib().b200_sharded_run(self._s, stream, float(alpha), _addr(B_slab), ldb or self.K, float(beta),
                                                _addr(C_slab) if C_slab is not None else None, ldc or self.M,
                                                _addr(D_slab), ldd or self.M, flags), "sharded_run")

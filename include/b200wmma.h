@@ -365,13 +365,23 @@ typedef struct b200_sharded b200_sharded;
 enum {
     B200_SHARDED_GATED = 1,       /* ONE launch of the gated GEMM (b200_gemm_f16f32_gated) instead of a
                                      few launches: overlaps transfer and main loop inside the kernel  */
-    B200_SHARDED_NO_TRANSFER = 2  /* A is already valid on this rank: the same launches without any copy
+    B200_SHARDED_NO_TRANSFER = 2, /* A is already valid on this rank: the same launches without any copy
                                      or wait (the compute-only time of a product)                     */
+    B200_SHARDED_NO_COMPUTE = 4   /* the transfer alone: every copy, flag and wait, no GEMM launch (the
+                                     transfer-only time of a product; D is not touched)               */
+};
+
+/* options of b200_sharded_set_option; set them on every rank alike, between products */
+enum {
+    B200_SHARDED_OPT_SCATTER_LANES = 0, /* streams rank 0 spreads its copies to different receivers over   */
+    B200_SHARDED_OPT_GATHER_LANES = 1,  /* streams every other rank spreads its forwarding copies over     */
+    B200_SHARDED_OPT_FIRST_GROUP = 2    /* panels in the first GEMM launch (later launches grow by 2.5x)   */
 };
 
 int b200_sharded_create(b200_sharded** out, b200_handle* h, int rank, int world, int64_t M, int64_t N,
                         int64_t K, int panels);
 int b200_sharded_destroy(b200_sharded* s);
+int b200_sharded_set_option(b200_sharded* s, int option, int64_t value);
 
 /* This rank's column slab [n0, n1) of B / C / D, its A buffer (M * K binary16) and flag block, and
  * how many transfer panels and GEMM launches a product takes.  Any out pointer may be NULL. */

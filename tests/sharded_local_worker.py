@@ -6,7 +6,7 @@ GPUs, only that every copy stays on this device.  No kernel ever waits for anoth
 launches sit behind stream-level waits, which is what makes this safe on a single GPU (the gated
 single-launch form polls from inside a kernel and is therefore not run here).
 
-    sharded_local_worker.py run <world> <M> <N> <K> <panels>      every rank's slab and A against the oracle
+    sharded_local_worker.py run <world> <M> <N> <K> <panels> [lanes]   every rank's slab and A against the oracle
     sharded_local_worker.py timeout                              a peer that never calls: deadline, error, context alive
 """
 import ctypes as C
@@ -48,7 +48,7 @@ def download(src_ptr, shape, dtype):
     return out
 
 
-def make_ranks(world, M, N, K, panels):
+def make_ranks(world, M, N, K, panels, lanes=1):
     handles = [Handle(0) for _ in range(world)]
     for h in handles:
         h.set_option(_lib.OPT_WAIT_BUDGET_NS, 500_000_000)
@@ -57,12 +57,16 @@ def make_ranks(world, M, N, K, panels):
     objs = [ShardedGemm(handles[r], M, N, K, rank=r, world=world, panels=panels) for r in range(world)]
     for o in objs:
         o.attach_local(objs)
+        if lanes > 1:  # copies to different receivers side by side, and a two-panel first launch
+            o.set_option(_lib.SHARDED_OPT_SCATTER_LANES, lanes)
+            o.set_option(_lib.SHARDED_OPT_GATHER_LANES, lanes)
+            o.set_option(_lib.SHARDED_OPT_FIRST_GROUP, 2)
     return handles, objs
 
 
-def run(world, M, N, K, panels):
+def run(world, M, N, K, panels, lanes=1):
     seed, alpha, beta = 4, 1.0, 1.0
-    handles, objs = make_ranks(world, M, N, K, panels)
+    handles, objs = make_ranks(world, M, N, K, panels, lanes)
     streams = [new_stream() for _ in range(world)]
     a_host = rng.matrix(seed, 0, M, K, rng.NORMAL, K ** -0.5, np.float16)
     upload(objs[0].a_ptr, a_host)
@@ -134,6 +138,6 @@ def timeout():
 
 if __name__ == "__main__":
     if sys.argv[1] == "run":
-        run(*(int(x) for x in sys.argv[2:7]))
+        run(*(int(x) for x in sys.argv[2:8]))
     else:
         timeout()
