@@ -401,6 +401,8 @@ def run_ours(args):
             sg.set_option(_lib.SHARDED_OPT_SCATTER_LANES, args.scatter_lanes)
             sg.set_option(_lib.SHARDED_OPT_GATHER_LANES, args.gather_lanes)
             sg.set_option(_lib.SHARDED_OPT_FIRST_GROUP, args.first_group)
+            if args.groups:
+                sg.set_groups([int(x) for x in args.groups.split(",")])
         n0, ns = sg.n0, sg.slab_cols
         A = torch.as_tensor(sg.a_view(), device=torch.device("cuda", local_rank))
         n_launches = 1 if args.gated else sg.n_groups
@@ -929,6 +931,7 @@ def main():
     ap.add_argument("--scatter-lanes", type=int, default=1, help="streams rank 0 spreads its copies over (sharded, p2p)")
     ap.add_argument("--gather-lanes", type=int, default=1, help="streams the other ranks spread their forwarding copies over (sharded, p2p)")
     ap.add_argument("--first-group", type=int, default=1, help="panels in the first GEMM launch (sharded, p2p)")
+    ap.add_argument("--groups", default=None, help="panels per GEMM launch, e.g. 1,2,3,3,3,4 (sharded, p2p)")
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="sharded runs: skip the end-to-end leg (experiments; the line then has e2e.value 0)")

@@ -68,6 +68,7 @@ SIGNATURES = {
     "b200_sharded_create": (_i, [_pp, _p, _i, _i, _i64, _i64, _i64, _i]),
     "b200_sharded_destroy": (_i, [_p]),
     "b200_sharded_set_option": (_i, [_p, _i, _i64]),
+    "b200_sharded_set_groups": (_i, [_p, _ip, _i]),
     "b200_sharded_info": (_i, [_p, C.POINTER(_i64), C.POINTER(_i64), _pp, _pp, _ip, _ip]),
     "b200_sharded_ipc_blob": (_i, [_p, _p]),
     "b200_sharded_attach": (_i, [_p, _p]),

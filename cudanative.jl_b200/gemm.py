@@ -294,6 +294,12 @@ class ShardedGemm:
         _lib.check(_lib.lib().b200_sharded_info(self._s, None, None, None, None, C.byref(n_p), C.byref(n_g)), "sharded_info")
         self.n_panels, self.n_groups = n_p.value, n_g.value
 
+    def set_groups(self, sizes) -> None:
+        """Panels per GEMM launch (b200_sharded_set_groups); must add up to ``n_panels``."""
+        arr = (C.c_int * len(sizes))(*[int(x) for x in sizes])
+        _lib.check(_lib.lib().b200_sharded_set_groups(self._s, arr, len(sizes)), "sharded_set_groups")
+        self.n_groups = len(sizes)
+
     def run(self, alpha: float, B_slab, beta: float, C_slab, D_slab, *, stream=None, gated: bool = False,
             no_transfer: bool = False, no_compute: bool = False, ldb: int | None = None, ldc: int | None = None, ldd: int | None = None) -> None:
         """Enqueue one product (b200_sharded_run).  B_slab: K x slab_cols, C_slab / D_slab: M x

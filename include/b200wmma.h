@@ -375,13 +375,18 @@ enum {
 enum {
     B200_SHARDED_OPT_SCATTER_LANES = 0, /* streams rank 0 spreads its copies to different receivers over   */
     B200_SHARDED_OPT_GATHER_LANES = 1,  /* streams every other rank spreads its forwarding copies over     */
-    B200_SHARDED_OPT_FIRST_GROUP = 2    /* panels in the first GEMM launch (later launches grow by 2.5x)   */
+    B200_SHARDED_OPT_FIRST_GROUP = 2    /* panels in the first GEMM launch (later launches grow by 1.4x up  */
+                                        /* to a quarter of the panels; see b200_sharded_set_groups)         */
 };
 
 int b200_sharded_create(b200_sharded** out, b200_handle* h, int rank, int world, int64_t M, int64_t N,
                         int64_t K, int panels);
 int b200_sharded_destroy(b200_sharded* s);
 int b200_sharded_set_option(b200_sharded* s, int option, int64_t value);
+/* The GEMM launches of a product as panel counts: launch i multiplies the next sizes[i] panels of A and
+ * starts once they have arrived.  The sizes must add up to the object's panel count (b200_sharded_info).
+ * Same on every rank, between products. */
+int b200_sharded_set_groups(b200_sharded* s, const int* sizes, int n);
 
 /* This rank's column slab [n0, n1) of B / C / D, its A buffer (M * K binary16) and flag block, and
  * how many transfer panels and GEMM launches a product takes.  Any out pointer may be NULL. */

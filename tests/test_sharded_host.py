@@ -50,8 +50,9 @@ def test_launch_groups_cover_the_panels_and_grow(lib, n):
     assert g[0][0] == 0 and g[-1][1] == n
     assert all(a1 == b0 and a1 > a0 for (a0, a1), (b0, _) in zip(g, g[1:]))
     sizes = [b - a for (a, b) in g]
-    assert sizes[0] == 1 and sizes == sorted(sizes) and len(g) <= 5
-    assert ShardLayout(8, 32768, 16384, 16).groups == [(0, 1), (1, 3), (3, 9), (9, 16)]
+    assert sizes[0] == 1 and max(sizes) <= max(1, n // 4) + 1  # no launch waits for more than about a quarter of A
+    assert all(y >= x for x, y in zip(sizes, sizes[1:-1]))       # growing, up to a merged or short last launch
+    assert [b - a for (a, b) in ShardLayout(8, 32768, 16384, 16).groups] == [1, 2, 2, 3, 4, 4]
 
 
 @pytest.mark.parametrize("world", [2, 3, 4, 8])
