@@ -27,7 +27,11 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
     return t;
 }
 
-__device__ __forceinline__ uint32_t lane_id() { return threadIdx.x & 31u; }
+__device__ __forceinline__ uint32_t lane_id() {
+    uint32_t l;
+    asm("mov.u32 %0, %%laneid;" : "=r"(l));
+    return l;
+}
 
 // ---------------------------------------------------------------------------------------------
 // mbarrier

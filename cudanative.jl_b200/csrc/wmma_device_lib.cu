@@ -50,7 +50,14 @@ __device__ __forceinline__ T* as_generic(const void* p) {
     return static_cast<T*>(const_cast<void*>(p));
 }
 
-__device__ __forceinline__ int lane() { return static_cast<int>(threadIdx.x & 31u); }
+// The hardware lane of the calling thread: right for any block shape (threadIdx.x & 31 would be wrong
+// for a block whose x extent is not a multiple of 32, e.g. threads = (16, 2)), as the reference's
+// intrinsics are (they are warp-level instructions, src/device/cuda/wmma.jl:500-504).
+__device__ __forceinline__ int lane() {
+    unsigned l;
+    asm("mov.u32 %0, %%laneid;" : "=r"(l));
+    return static_cast<int>(l);
+}
 
 __device__ __forceinline__ __half half_of(uint32_t word, int hi) {
     return __ushort_as_half(static_cast<unsigned short>(hi ? (word >> 16) : (word & 0xffffu)));

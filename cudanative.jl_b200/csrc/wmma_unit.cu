@@ -155,7 +155,10 @@ __global__ void __launch_bounds__(128) unit_tcgen05_kernel(UnitArgs u, int* stat
         mbar_init(smem_u32(&bar), 1);
         fence_mbar_init();
     }
-    if (warp == 0) tmem_alloc<1>(smem_u32(&tmem_slot), 32);
+    if (warp == 0) {
+        __syncwarp();  // thread 0 took the branch above: the allocation is warp-collective (.sync.aligned)
+        tmem_alloc<1>(smem_u32(&tmem_slot), 32);
+    }
 
     auto core_off = [](int r, int k) { return (r >> 3) * 256 + (k >> 3) * 128 + (r & 7) * 16 + (k & 7) * 2; };
     {

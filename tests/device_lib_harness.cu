@@ -97,3 +97,15 @@ extern "C" int harness_run(int a_row, int b_row, int c_row, int d_row, int c_f16
     if (e != cudaSuccess) return static_cast<int>(e);
     return static_cast<int>(cudaDeviceSynchronize());
 }
+
+// The same one-warp kernel launched as a 16 x 2 block: the warp's lanes are then NOT threadIdx.x & 31.
+// Generic and global address spaces only (the shared-memory staging above strides by threadIdx.x).
+extern "C" int harness_run_block16x2(int a_row, int b_row, int c_row, int d_row, int c_f16, int d_f16, int as, const void* a,
+                                     const void* b, const void* c, void* d) {
+    if (as == 3) return static_cast<int>(cudaErrorInvalidValue);
+    Sel s{a_row, b_row, c_row, d_row, c_f16, d_f16, as};
+    harness_kernel<<<1, dim3(16, 2, 1)>>>(s, a, b, c, d);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return static_cast<int>(e);
+    return static_cast<int>(cudaDeviceSynchronize());
+}

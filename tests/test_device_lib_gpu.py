@@ -71,6 +71,8 @@ def harness(pkg):
     lib = C.CDLL(str(HARNESS))
     lib.harness_run.restype = C.c_int
     lib.harness_run.argtypes = [C.c_int] * 7 + [C.c_void_p] * 4
+    lib.harness_run_block16x2.restype = C.c_int
+    lib.harness_run_block16x2.argtypes = [C.c_int] * 7 + [C.c_void_p] * 4
     return lib
 
 
@@ -90,6 +92,24 @@ def test_all_layouts_and_types_through_the_linked_functions(harness, oracle, as_
         assert rc == 0, f"cudaError {rc}"
         ref = oracle.wmma_unit_ref(a, b, c, a_layout=ar, b_layout=br, c_layout=cr, d_layout=dr, d_type=dt)
         assert oracle.unit_close(Array(d_dev), ref), f"case {i}: layouts {ar}{br}{cr}{dr} C {ct.__name__} D {dt.__name__}"
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("as_", [0, 1], ids=["generic", "global"])
+def test_any_block_shape_like_the_reference_intrinsics(harness, oracle, as_):
+    """The reference's fragment operations are warp-level instructions and work in a block of any shape;
+    a kernel launched with threads = (16, 2) has lanes that are not threadIdx.x & 31.  All 16 layout
+    combinations through the linked functions in such a block."""
+    for i, (ar, br, cr, dr) in enumerate(itertools.product([0, 1], [0, 1], [0, 1], [0, 1])):
+        a = rng.matrix(600 + i, 0, 16, 16, rng.UNIFORM, 1.0, np.float16)
+        b = rng.matrix(600 + i, 1, 16, 16, rng.UNIFORM, 1.0, np.float16)
+        c = rng.matrix(600 + i, 2, 16, 16, rng.UNIFORM, 1.0, np.float32)
+        a_dev, b_dev, c_dev = CuArray(a), CuArray(b), CuArray(c)
+        d_dev = CuArray(np.zeros((16, 16), dtype=np.float32, order="F"))
+        rc = harness.harness_run_block16x2(ar, br, cr, dr, 0, 0, as_, a_dev.ptr, b_dev.ptr, c_dev.ptr, d_dev.ptr)
+        assert rc == 0, f"cudaError {rc}"
+        ref = oracle.wmma_unit_ref(a, b, c, a_layout=ar, b_layout=br, c_layout=cr, d_layout=dr, d_type=np.float32)
+        assert oracle.unit_close(Array(d_dev), ref), f"case {i}: layouts {ar}{br}{cr}{dr} in a 16 x 2 block"
 
 
 @pytest.mark.gpu
