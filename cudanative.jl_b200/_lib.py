@@ -18,7 +18,7 @@ MATRIX_A, MATRIX_B, ACCUMULATOR = 0, 1, 2
 LOWER_WARP, LOWER_TCGEN05 = 0, 1
 KERNEL_AUTO, KERNEL_TCGEN05, KERNEL_SIMPLE = 0, 1, 2
 (OPT_FORCE_KERNEL, OPT_MAX_CTAS, OPT_WAIT_BUDGET_NS, OPT_TILE_N, OPT_SPLIT_K, OPT_CTA_PAIR,
- OPT_RASTER_GROUP, OPT_CHECK_ON_CALL, OPT_PDL) = range(9)
+ OPT_RASTER_GROUP, OPT_CHECK_ON_CALL, OPT_PDL, OPT_F16_ACCUMULATE) = range(10)
 SHARDED_GATED, SHARDED_NO_TRANSFER, SHARDED_NO_COMPUTE = 1, 2, 4
 SHARDED_OPT_SCATTER_LANES, SHARDED_OPT_GATHER_LANES, SHARDED_OPT_FIRST_GROUP = 0, 1, 2
 SHARDED_MAX_RANKS, SHARDED_MAX_PANELS, SHARDED_BLOB_BYTES = 64, 32, 128

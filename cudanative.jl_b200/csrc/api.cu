@@ -121,6 +121,15 @@ int gemm_dispatch(b200_handle* h, cudaStream_t stream, const GemmProblem& g) {
     if ((rc = check_current_device(h))) return rc;
     std::string why;
     const bool eligible = gemm_tcgen05_eligible(g, &why);
+    if (g.acc_f16) {
+        // only the tensor-core kernel has a binary16 accumulator; the plain kernel and the split-K reduction sum in binary32
+        if (!eligible) return fail(B200_UNSUPPORTED, "Float16 accumulation needs the tcgen05 kernel: " + why);
+        if (g.K == 0) return fail(B200_UNSUPPORTED, "Float16 accumulation needs K > 0");
+        if (h->force_kernel == B200_KERNEL_SIMPLE) return fail(B200_UNSUPPORTED, "Float16 accumulation: the plain kernel accumulates in Float32");
+        GemmPlan plan = make_plan(h, g);
+        plan.split_k = 1;
+        return gemm_tcgen05_launch(g, plan, nullptr, h->status_word, h->sm_count, stream, &h->last);
+    }
     int kernel = h->force_kernel;
     const int64_t m_quant = 16 / elem_bytes(g.d_type);
     if (kernel == B200_KERNEL_AUTO && !eligible && (g.M % m_quant) && g.M > m_quant && !g.panel_flags) {
@@ -349,6 +358,10 @@ int b200_set_option(b200_handle* h, int option, int64_t value) {
             if (value != 0 && value != 1) return fail(B200_INVALID_ARG, "pdl must be 0 or 1");
             h->pdl = static_cast<int>(value);
             return B200_OK;
+        case B200_OPT_F16_ACCUMULATE:
+            if (value != 0 && value != 1) return fail(B200_INVALID_ARG, "f16_accumulate must be 0 or 1");
+            h->f16_accumulate = static_cast<int>(value);
+            return B200_OK;
         default:
             return fail(B200_INVALID_ARG, "unknown option");
     }
@@ -366,6 +379,7 @@ int b200_get_option(b200_handle* h, int option, int64_t* value) {
         case B200_OPT_RASTER_GROUP: *value = h->raster_group; return B200_OK;
         case B200_OPT_CHECK_ON_CALL: *value = h->check_on_call; return B200_OK;
         case B200_OPT_PDL: *value = h->pdl; return B200_OK;
+        case B200_OPT_F16_ACCUMULATE: *value = h->f16_accumulate; return B200_OK;
         default: return fail(B200_INVALID_ARG, "unknown option");
     }
 }
@@ -418,6 +432,9 @@ int b200_gemm_f16_typed(b200_handle* h, b200_stream stream, int transA, int tran
                   static_cast<float*>(D), ldd};
     g.c_type = c_type;
     g.d_type = d_type;
+    // Config{16, 16, 16, Float16} with a Float16 C: the .f16.f16 mma variants of the reference
+    // (src/device/cuda/wmma.jl:222-257) accumulate in binary16
+    g.acc_f16 = (h->f16_accumulate && c_type == B200_F16 && d_type == B200_F16) ? 1 : 0;
     return gemm_entry(h, static_cast<cudaStream_t>(stream), g);
 }
 

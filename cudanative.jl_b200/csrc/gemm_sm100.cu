@@ -315,6 +315,7 @@ int gemm_tcgen05_launch(const GemmProblem& g, const GemmPlan& plan, float* scrat
     p.status = status_word;
     p.wait_budget_ns = plan.wait_budget_ns;
     p.ab_bf16 = g.ab_type == B200_BF16 ? 1 : 0;
+    p.acc_f16 = g.acc_f16 ? 1 : 0;
     p.batch = static_cast<int>(g.batch);
 
     if (q.split_k > 1) {

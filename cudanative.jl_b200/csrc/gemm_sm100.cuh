@@ -54,6 +54,7 @@ struct GemmParams {
     int kb_per_panel;
     int c_fmt, d_fmt;      // element types of C and D in memory: 0 = binary32, 1 = binary16, 2 = bfloat16
     int ab_bf16;           // A and B are bfloat16 instead of binary16
+    int acc_f16;           // accumulate in binary16 (tensor memory then holds one binary16 value per 32-bit cell)
     int batch;             // matrices per launch (kBatch kernels; the tensor maps are 3-D then)
     int* status;
     unsigned long long wait_budget_ns;
@@ -297,9 +298,8 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0 && cta_rank == 0) {
-            const uint32_t idesc = p.ab_bf16
-                ? make_idesc_f16_f32(Cfg::BM * kCtas, kBN, kAMn ? 1 : 0, kBMn ? 1 : 0, 1)
-                : make_idesc_f16_f32(Cfg::BM * kCtas, kBN, kAMn ? 1 : 0, kBMn ? 1 : 0, 0);
+            const uint32_t idesc = make_idesc_f16_f32(Cfg::BM * kCtas, kBN, kAMn ? 1 : 0, kBMn ? 1 : 0, p.ab_bf16 ? 1 : 0,
+                                                      p.acc_f16 ? 1 : 0);
             // Descriptors differ between stages and k-steps only in their start-address field
             // (bits [0,14), in units of 16 bytes): build them once and add offsets.
             // K-major tile: rows of 128 B, 8-row groups 1 KiB apart, k = 16 advances 32 B inside
@@ -352,6 +352,7 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         const float alpha = p.alpha, beta = p.beta;
         const bool c_half = p.c_fmt != 0, d_half = p.d_fmt != 0;  // 2-byte elements
         const bool c_bf16 = p.c_fmt == 2, d_bf16 = p.d_fmt == 2;
+        const bool acc_f16 = p.acc_f16 != 0;
         const uint32_t c_chunk_bytes = c_half ? Cfg::EPI_BYTES / 2 : Cfg::EPI_BYTES;
         // C is updated in place in the staging buffer only if D has the same element size; otherwise
         // every thread must have read its C values before anybody writes D over them
@@ -414,6 +415,11 @@ gemm_f16f32_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 if (ok) {
                     tmem_ld_32x32b_x32(tmem_base + lane_base + acc * kBN + j * Cfg::EPI_COLS, r);
                     tmem_wait_ld();
+                    if (acc_f16) {  // a binary16 accumulator sits in the low half of its 32-bit cell
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            r[i] = __float_as_uint(__half2float(__ushort_as_half(static_cast<unsigned short>(r[i] & 0xffffu))));
+                    }
                     if (has_c) {
                         if (c_bf16) {
 #pragma unroll

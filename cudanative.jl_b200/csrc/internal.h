@@ -44,6 +44,8 @@ struct GemmProblem {
     int d_type = B200_F32;
     // element type of A and B: B200_F16 or B200_BF16 (both operands the same)
     int ab_type = B200_F16;
+    // accumulate in binary16 instead of binary32 (tcgen05 kernel only; Float16 A, B, C and D)
+    int acc_f16 = 0;
     // batched problems: `batch` independent products; matrix i of X starts stride_x * i elements after
     // X (a stride of 0 repeats the matrix).  batch == 1 ignores the strides.
     int64_t batch = 1;
@@ -85,6 +87,7 @@ struct b200_handle {
     int raster_group = 0;
     int check_on_call = 0;
     int pdl = 1;
+    int f16_accumulate = 0;
     // workspace of the host-buffer entry point and split-K scratch (grown on demand)
     void* ws[4] = {nullptr, nullptr, nullptr, nullptr};
     size_t ws_bytes[4] = {0, 0, 0, 0};

@@ -420,12 +420,12 @@ __device__ __forceinline__ void tc_fence_after_sync() {
 // tcgen05: descriptors
 // ---------------------------------------------------------------------------------------------
 // Instruction descriptor of tcgen05.mma.kind::f16 with binary16 (or, ab_bf16 = 1, bfloat16) A and
-// B and a binary32 accumulator.  Bit layout (PTX ISA, "Instruction descriptor"): [4,6) D format
-// (1 = F32), [7,10) A format (0 = F16, 1 = BF16), [10,13) B format, [15] A major (0 = K, 1 = MN), [16] B major,
+// B and a binary32 (or, d_f16 = 1, binary16) accumulator.  Bit layout (PTX ISA, "Instruction descriptor"): [4,6) D format
+// (0 = F16, 1 = F32), [7,10) A format (0 = F16, 1 = BF16), [10,13) B format, [15] A major (0 = K, 1 = MN), [16] B major,
 // [17,23) N >> 3, [24,29) M >> 4.
 __host__ __device__ constexpr uint32_t make_idesc_f16_f32(int m, int n, int a_mn_major,
-                                                          int b_mn_major, int ab_bf16 = 0) {
-    return (1u << 4) | (static_cast<uint32_t>(ab_bf16) << 7) | (static_cast<uint32_t>(ab_bf16) << 10) | (static_cast<uint32_t>(a_mn_major) << 15) |
+                                                          int b_mn_major, int ab_bf16 = 0, int d_f16 = 0) {
+    return ((d_f16 ? 0u : 1u) << 4) | (static_cast<uint32_t>(ab_bf16) << 7) | (static_cast<uint32_t>(ab_bf16) << 10) | (static_cast<uint32_t>(a_mn_major) << 15) |
            (static_cast<uint32_t>(b_mn_major) << 16) | (static_cast<uint32_t>(n >> 3) << 17) |
            (static_cast<uint32_t>(m >> 4) << 24);
 }

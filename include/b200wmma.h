@@ -66,6 +66,12 @@ enum {
     B200_OPT_SPLIT_K = 4,        /* 0 = auto, 1 = off, n>1 = split the K loop n ways              */
     B200_OPT_CTA_PAIR = 5,       /* 0 = auto, 1 = one-CTA tiles only, 2 = force 2-CTA tiles       */
     B200_OPT_RASTER_GROUP = 6,   /* tile rows per rasterisation group (0 = default)               */
+    B200_OPT_F16_ACCUMULATE = 9, /* 1 = b200_gemm_f16_typed with Float16 C AND Float16 D accumulates in     */
+                                 /* binary16 on the tensor cores, as WMMA.mma does for Config{16,16,16,    */
+                                 /* Float16} with a Float16 accumulator fragment (the .f16.f16 variants,   */
+                                 /* src/device/cuda/wmma.jl:222-257).  Default 0: binary32 accumulation,  */
+                                 /* Float16 only as the storage type.  tcgen05 kernel only (UNSUPPORTED    */
+                                 /* for shapes it cannot take); the split-K option is ignored.            */
     B200_OPT_PDL = 8,            /* 1 (default) = tcgen05 GEMM kernels are launched with programmatic   */
                                  /* stream serialization: their set-up overlaps the tail of the kernel  */
                                  /* before them in the stream; 0 = ordinary launches                    */

@@ -138,6 +138,29 @@ def gemm_ref(transA: bool, transB: bool, alpha: float, A16: np.ndarray, B16: np.
     return np.asfortranarray(D.astype(np.float32))
 
 
+def gemm_ref_f16acc(transA: bool, transB: bool, alpha: float, A16: np.ndarray, B16: np.ndarray, beta: float, C16,
+                    block: int = 16):
+    """The product with a binary16 accumulator, as the reference's ``Config{16, 16, 16, Float16}`` with a
+    Float16 accumulator fragment computes it when a caller loops over K (the .f16.f16 mma variants,
+    src/device/cuda/wmma.jl:222-257 of CUDAnative.jl; its test accepts rtol = sqrt(eps(Float16)),
+    test/device/wmma.jl:243-246): the running sum is rounded to binary16 after every ``block`` (= the
+    instruction's K, 16) products; inside a block the products are summed in binary32.  alpha and beta
+    are applied in binary32 and the result is rounded to binary16 once.  Hardware may round inside a
+    block differently, hence the tolerance the tests state."""
+    opA = (A16.T if transA else A16).astype(np.float32)
+    opB = (B16.T if transB else B16).astype(np.float32)
+    M, K = opA.shape
+    N = opB.shape[1]
+    acc = np.zeros((M, N), dtype=np.float16)
+    for k0 in range(0, K, block):
+        part = opA[:, k0:k0 + block] @ opB[k0:k0 + block, :]
+        acc = (acc.astype(np.float32) + part).astype(np.float16)
+    D = np.float32(alpha) * acc.astype(np.float32)
+    if C16 is not None and beta != 0.0:
+        D = D + np.float32(beta) * C16.astype(np.float32)
+    return np.asfortranarray(D.astype(np.float16))
+
+
 def errors(D: np.ndarray, ref: np.ndarray) -> tuple[float, float]:
     """(relative Frobenius error, max over elements of |D-ref| / (|ref|+1))."""
     D64 = D.astype(np.float64)

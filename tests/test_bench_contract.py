@@ -61,3 +61,42 @@ def test_reference_arm_prints_one_contract_line():
     assert d["config"]["workload"] == "gemm4096" and d["data"] == "synthetic"
     assert d["e2e"] == {"value": d["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
     assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["cores"] >= 1 and "sgemm" in d["cpu_baseline"]["sample"]
+
+
+def test_sampled_tile_check_accepts_a_right_slab_and_names_a_wrong_one():
+    """bench.check_slab_tiles (the parity leg of every sharded run) on the CPU: a slab computed by the
+    oracle passes with all ten tiles looked at; one spoiled element in the slab's last column, or a
+    spoiled column of A, fails with the place in the message."""
+    import numpy as np
+    import torch
+
+    import __graft_entry__ as entry
+
+    oracle, rng = entry.load_oracle(), entry.load_package().rng
+    w = dict(M=256, N=384, K=128, transA=False, transB=False, alpha=1.0, beta=1.0, seed=4, b_rsqrt=True, c_dist="normal")
+    n0, ns = 128, 256  # the middle of three slabs
+    a = rng.matrix(w["seed"], 0, w["M"], w["K"], rng.NORMAL, w["K"] ** -0.5, np.float16)
+    b = rng.window(w["seed"], 1, w["K"], 0, w["K"], n0, n0 + ns, rng.NORMAL, w["K"] ** -0.5, np.float16)
+    c = rng.window(w["seed"], 2, w["M"], 0, w["M"], n0, n0 + ns, rng.NORMAL, 1.0, np.float32)
+    d = oracle.gemm_ref(False, False, 1.0, a, b, 1.0, c)
+    D = torch.from_numpy(np.ascontiguousarray(d.T)).reshape(-1)      # column-major slab, as the device holds it
+    A = torch.from_numpy(np.ascontiguousarray(a.T)).reshape(-1)
+    ok = bench.check_slab_tiles(w, D, n0, ns, A=A)
+    assert ok["ok"] and ok["tiles"] == 10 and ok["a_columns"] >= 2 and ok["rel_fro_max"] < 1e-5
+    bad = D.clone()
+    bad.view(ns, w["M"])[ns - 1, :] += 1.0                           # the slab's last column
+    out = bench.check_slab_tiles(w, bad, n0, ns)
+    assert not out["ok"] and "tile rows" in out["why"]
+    bad_a = A.clone()
+    bad_a.view(w["K"], w["M"])[w["K"] - 1, 5] = 0.25
+    out = bench.check_slab_tiles(w, D, n0, ns, A=bad_a)
+    assert not out["ok"] and "column 127 of A" in out["why"]
+    assert bench.check_slab_tiles(w, D, n0, 0)["tiles"] == 0         # a rank without columns has nothing to check
+
+
+def test_host_threads_are_raised_past_a_one_thread_environment(monkeypatch):
+    """torchrun exports OMP_NUM_THREADS=1 to its ranks; the CPU arm sets the BLAS pool itself and reports it."""
+    import os
+
+    monkeypatch.setenv("OMP_NUM_THREADS", "1")
+    assert bench.use_all_host_threads() == (os.cpu_count() or 1)

@@ -402,6 +402,48 @@ def test_bounded_wait_reports_and_context_survives(handle, oracle):
     oracle.assert_close(d, oracle.gemm_ref(False, False, 1.0, a, b, 1.0, c), "after timeout")
 
 
+@pytest.mark.parametrize("tA,tB,M,N,K", [(False, False, 256, 256, 512), (True, False, 512, 384, 2048), (False, True, 384, 512, 1000)])
+def test_float16_accumulation_for_whole_matrices(handle, oracle, tA, tB, M, N, K):
+    """B200_OPT_F16_ACCUMULATE: Config{16,16,16,Float16} with a Float16 accumulator (the .f16.f16 mma
+    variants, src/device/cuda/wmma.jl:222-257) for whole matrices -- the tensor cores accumulate in
+    binary16.  Inputs are non-negative so that the running sums grow and binary16 accumulation shows.
+    Tolerances, written out: against the binary32 product every element within sqrt(eps(Float16)) (the
+    reference's rtol, test/device/wmma.jl:243-246) of |ref| + rms(ref); against the blockwise binary16
+    statement of the oracle a relative Frobenius error of at most 5e-3; and the result must be further
+    from the binary32 product than the default (binary32 accumulation, rounded once) is."""
+    force(handle, _lib.KERNEL_TCGEN05)
+    a, b, c32 = operands(M, N, K, tA, tB, seed=77, a_scale=1.0)
+    a, b = np.abs(a) * np.float16(0.25), np.abs(b) * np.float16(0.25)
+    c = np.asfortranarray(c32.astype(np.float16))
+    a_dev, b_dev, c_dev = CuArray(a), CuArray(b), CuArray(c)
+    ref32 = oracle.gemm_ref(tA, tB, 1.0, a, b, 0.5, c)
+    out = {}
+    for mode in (0, 1):
+        handle.set_option(_lib.OPT_F16_ACCUMULATE, mode)
+        d_dev = CuHostArray(np.float16, shape=(M, N))
+        handle.gemm_typed(tA, tB, M, N, K, 1.0, a_dev, a.shape[0], b_dev, b.shape[0], 0.5, c_dev, M, np.float16, d_dev, M, np.float16)
+        _lib.check(_lib.lib().b200_stream_sync(None), "sync")
+        assert handle.device_status()[0] == 0
+        out[mode] = Array(d_dev).astype(np.float32)
+    handle.set_option(_lib.OPT_F16_ACCUMULATE, 0)
+    rms = float(np.sqrt(np.mean(ref32.astype(np.float64) ** 2)))
+    assert np.all(np.abs(out[1] - ref32) <= oracle.UNIT_RTOL * (np.abs(ref32) + rms)), "outside the reference's rtol"
+    ref16 = oracle.gemm_ref_f16acc(tA, tB, 1.0, a, b, 0.5, c).astype(np.float32)
+    rel16, _ = oracle.errors(out[1], ref16)
+    assert rel16 <= 5e-3, f"relative Frobenius error {rel16:.2e} against the binary16-accumulating oracle"
+    err_f32acc, _ = oracle.errors(out[0], ref32)
+    err_f16acc, _ = oracle.errors(out[1], ref32)
+    assert err_f32acc <= 4e-4 and err_f16acc > 1.5 * err_f32acc, (err_f32acc, err_f16acc)
+    # a Float32 C or D keeps binary32 accumulation whatever the option says; shapes the TMA kernel cannot take are refused
+    from cudanative_jl_b200 import B200Error
+    handle.set_option(_lib.OPT_F16_ACCUMULATE, 1)
+    force(handle, _lib.KERNEL_AUTO)
+    with pytest.raises(B200Error, match="Float16 accumulation needs the tcgen05 kernel"):
+        handle.gemm_typed(tA, tB, M - 3, N, K, 1.0, a_dev, a.shape[0], b_dev, b.shape[0], 0.5, c_dev, M, np.float16,
+                          CuHostArray(np.float16, shape=(M, N)), M, np.float16)
+    handle.set_option(_lib.OPT_F16_ACCUMULATE, 0)
+
+
 def test_check_on_call_finds_an_earlier_failure_at_the_next_call(handle, oracle):
     """B200_OPT_CHECK_ON_CALL: like the reference's exception flag, polled at every API call
     (src/init.jl:37, src/exceptions.jl:76-89 of CUDAnative.jl), a wait that ran out in an earlier,
