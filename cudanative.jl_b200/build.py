@@ -71,7 +71,10 @@ def build(force: bool = False, verbose: bool = False) -> Path:
                     print(out)
     objs = [BUILD_DIR / (s + ".o") for s in SOURCES]
     if force or jobs or _stale(LIB_PATH, objs):
-        run([nvcc, "-Wno-deprecated-gpu-targets", "-shared", "-o", str(LIB_PATH), *map(str, objs), "-lcudart"])
+        # link beside the target and rename: a reader (a loader, a copy of the tree) never sees half a library
+        tmp = LIB_PATH.with_suffix(".so.tmp")
+        run([nvcc, "-Wno-deprecated-gpu-targets", "-shared", "-o", str(tmp), *map(str, objs), "-lcudart"])
+        os.replace(tmp, LIB_PATH)
     return LIB_PATH
 
 

@@ -488,7 +488,11 @@ int b200_sharded_run(b200_sharded* s, b200_stream stream, float alpha, const voi
     const int64_t M = s->M, K = s->K;
     const bool transfer = s->world > 1 && !(flags & B200_SHARDED_NO_TRANSFER);
     const bool gated = transfer && (flags & B200_SHARDED_GATED);
+    // everything that could make a launch fail is looked at BEFORE the first copy or flag is enqueued: a rank
+    // that gave up half-way would leave its peers waiting for words it never writes
     if (ns > 0 && (!B_slab || !D_slab || (beta != 0.0f && !C_slab))) return fail(B200_INVALID_ARG, "sharded_run: null slab pointer");
+    if (ns > 0 && (ldb < K || ldd < M || (beta != 0.0f && ldc < M)))
+        return fail(B200_INVALID_ARG, "sharded_run: leading dimension smaller than the rows of the slab (ldb >= K, ldc and ldd >= M)");
     const __half* a = static_cast<const __half*>(s->a_local);
     const __half* b = static_cast<const __half*>(B_slab);
     if (transfer) {

@@ -15,6 +15,8 @@
 // stay consistent.
 #include <cuda_fp16.h>
 
+#include <mutex>
+
 #include "ptx_sm100.cuh"
 #include "wmma_frag.cuh"
 #include "internal.h"
@@ -229,9 +231,13 @@ int check_type(int t, const char* what) {
 }
 
 // device status word for the tcgen05 unit (one per process and device is enough: the unit is a
-// single CTA and the word only ever holds the first failure)
+// single CTA and the word only ever holds the first failure).  16 bytes per device, kept until the
+// process exits; the table is guarded because WMMA calls may come from several host threads
+// (the reference's @cuda is thread-safe, test/device/execution.jl:1057-1078).
 int* unit_status_word() {
     static int* word[64] = {};
+    static std::mutex guard;
+    std::lock_guard<std::mutex> lock(guard);
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
     if (!word[dev]) {

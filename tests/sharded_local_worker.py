@@ -108,6 +108,19 @@ def timeout():
     M, N, K = 256, 512, 256
     handles, objs = make_ranks(2, M, N, K, 2)
     o = objs[1]
+    # argument checks come before anything is enqueued (a rank that gave up half-way would strand its peers)
+    for bad in ([1], [1, 2], [0, 2]):
+        try:
+            o.set_groups(bad)
+            raise SystemExit(f"launch groups {bad} were accepted for {o.n_panels} panels")
+        except B200Error as e:
+            assert e.status == _lib.INVALID_ARG, e
+    o.set_groups([1, 1])
+    try:
+        o.run(1.0, 0x1000, 0.0, None, 0x2000, stream=None, ldb=K - 8)
+        raise SystemExit("a leading dimension smaller than K was accepted")
+    except B200Error as e:
+        assert e.status == _lib.INVALID_ARG and "leading dimension" in str(e), e
     s = new_stream()
     b = rng.matrix(9, 1, K, o.slab_cols, rng.NORMAL, 1.0, np.float16)
     b_dev = CuArray(b)
