@@ -609,8 +609,8 @@ def run_ours(args):
         "e2e": {"value": round(e2e_tflops, 3), "unit": "TFLOP/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
                 "steps": e2e_steps, "api": "b200_sharded_run + pinned copies" if sharded else "b200_gemm_f16f32_host"},
         "gpu_launches": launches_per_step * args.steps * world,
-        # traffic: DRAM bytes per launch come from an ncu capture; none has been taken of this build's kernel
-        # inside this run, so the line does not claim one (the summaries under profiles/ say which build they saw)
+        # traffic: DRAM bytes per launch come from an ncu capture; none is taken inside a bench run, so the line
+        # does not claim one
         "roofline": {"bound": "hbm" if hbm_bound else "tensor", "achieved": round(achieved, 2), "peak": peak, "unit": unit,
                      "frac": round(achieved / peak, 4), "traffic": None, "peak_source": f"{peaks['source']} ({peak_kind})",
                      "nominal_frac": round(achieved / (8000.0 if hbm_bound else 2250.0), 4),
