@@ -218,6 +218,32 @@ def test_deterministic(handle):
     assert np.array_equal(d1, d2)
 
 
+def test_back_to_back_launches_with_and_without_programmatic_launch(handle, oracle):
+    """B200_OPT_PDL: the kernel's set-up may overlap the tail of the kernel before it; its global accesses
+    may not.  Ten dependent launches in a row (each reads the D of the one before as its C) give the same
+    bits with the option on (default) and off, and the right numbers."""
+    force(handle, _lib.KERNEL_TCGEN05)
+    M, N, K = 512, 768, 256
+    a, b, c = operands(M, N, K, True, False, seed=92)
+    a_dev, b_dev = CuArray(a), CuArray(b)
+    assert handle.get_option(_lib.OPT_PDL) == 1
+    out = {}
+    for pdl in (1, 0):
+        handle.set_option(_lib.OPT_PDL, pdl)
+        d_dev = CuArray(c)
+        for _ in range(10):  # D <- 0.5 * A B + 0.5 * D, in place
+            handle.gemm(True, False, M, N, K, 0.5, a_dev, K, b_dev, K, 0.5, d_dev, M, d_dev, M)
+        _lib.check(_lib.lib().b200_stream_sync(None), "sync")
+        assert handle.device_status()[0] == 0
+        out[pdl] = Array(d_dev)
+    handle.set_option(_lib.OPT_PDL, 1)
+    assert np.array_equal(out[0], out[1])
+    ref = c
+    for _ in range(10):
+        ref = oracle.gemm_ref(True, False, 0.5, a, b, 0.5, ref)
+    oracle.assert_close(out[1], ref, "ten dependent launches")
+
+
 def test_config2_4096_cubed(handle, oracle):
     """Benchmark config 2: M=N=K=4096, A, B column-major normal/sqrt(K), C normal, alpha=beta=1, seed 1."""
     force(handle, _lib.KERNEL_AUTO)
