@@ -170,3 +170,27 @@ def test_broadcast_flow_on_gloo(world, shape):
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert r.stdout.count(" ok: slab") == world
+
+
+def _fake_ranks(mode, world=2):
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+           "--master-port", str(29540 + world + (7 if mode == "silent" else 0)), str(ROOT / "tests" / "sharded_fake_worker.py"), mode]
+    return subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env)
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_thin_caller_from_separate_processes_on_gloo(world):
+    """ShardedGemm in `world` real processes against a Python stand-in for the library: blobs exchanged in
+    rank order, slab pointers and leading dimensions as declared, every slab against the oracle."""
+    r = _fake_ranks("run", world)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count(" ok: slab") == world
+
+
+def test_a_rank_that_never_calls_is_reported_on_the_host():
+    """Failure detection made on the host: rank 1 of 2 never makes its call; rank 0's wait comes back with
+    B200_PEER_TIMEOUT after its deadline and names the silent peer.  No GPU, nothing hangs."""
+    r = _fake_ranks("silent")
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "rank 0 saw PEER_TIMEOUT" in r.stdout and "rank 1 stayed silent" in r.stdout
