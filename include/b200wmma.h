@@ -157,7 +157,8 @@ int b200_gemm_f16f32(b200_handle* h, b200_stream stream, int transA, int transB,
 /* b200_gemm_f16f32 with the element types of C and D chosen per call (B200_F16 or B200_F32): the
  * four accumulator / result type combinations WMMA.Config{16,16,16,d_type} and load_c offer
  * (src/device/cuda/wmma.jl:23-30, :394; all four are swept by test/device/wmma.jl:188-248).
- * Accumulation is binary32 in every case; a binary16 C is widened when it is read and a binary16
+ * Accumulation is binary32 in every case unless B200_OPT_F16_ACCUMULATE is set (then binary16
+ * for Float16 C with Float16 D); a binary16 C is widened when it is read and a binary16
  * D is rounded once (to nearest even) when it is written.  ldc / ldd count elements of the
  * respective type.  TMA path: ldc / ldd multiples of 16 bytes, and whole 16-byte chunks of rows
  * (M % 8 for a binary16 D); the remaining rows run on the simple kernel. */
