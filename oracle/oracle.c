@@ -166,6 +166,35 @@ void oracle_gemm(int transA, int transB, int64_t M, int64_t N, int64_t K, float 
         }
 }
 
+/* ---- the same product with a binary16 accumulator ------------------------------------------- */
+/* What a caller of the reference gets who loops WMMA.mma over K with Config{16, 16, 16, Float16} and a
+ * Float16 accumulator fragment (the .f16.f16 variants, src/device/cuda/wmma.jl:222-257): the running
+ * sum is rounded to binary16 after every `block` products (16 = the instruction's K).  Inside a block
+ * the products are summed in double and rounded once -- the hardware's order inside one instruction is
+ * not specified, the reference's own test allows rtol = sqrt(eps(Float16)) (test/device/wmma.jl:243-246).
+ * alpha and beta are applied in binary32 and D is rounded to binary16 once. */
+void oracle_gemm_f16acc(int transA, int transB, int64_t M, int64_t N, int64_t K, float alpha, const float* A, int64_t lda,
+                        const float* B, int64_t ldb, float beta, const float* C, int64_t ldc, float* D, int64_t ldd,
+                        int block) {
+    if (block < 1) block = 16;
+    for (int64_t n = 0; n < N; ++n)
+        for (int64_t m = 0; m < M; ++m) {
+            float acc = 0.0f; /* always a binary16 value */
+            for (int64_t k0 = 0; k0 < K; k0 += block) {
+                double part = 0.0;
+                for (int64_t k = k0; k < K && k < k0 + block; ++k) {
+                    const float a = transA ? A[k + m * lda] : A[m + k * lda];
+                    const float b = transB ? B[n + k * ldb] : B[k + n * ldb];
+                    part += (double)a * (double)b;
+                }
+                acc = oracle_round_f16((float)((double)acc + part));
+            }
+            float v = alpha * acc;
+            if (beta != 0.0f) v += beta * C[m + n * ldc];
+            D[m + n * ldd] = oracle_round_f16(v);
+        }
+}
+
 /* ---- the 16x16x16 unit as the reference's test states it ----------------------------------- */
 /* a, b: 16x16 binary16 values as float in their STORED order with leading dimension 16;
  * layouts 0 = ColMajor, 1 = RowMajor (stored matrix is the transpose).  c_is_f16 / d_is_f16

@@ -69,6 +69,9 @@ def clib() -> C.CDLL:
         L.oracle_gemm.restype = None
         L.oracle_gemm.argtypes = [C.c_int, C.c_int, C.c_int64, C.c_int64, C.c_int64, C.c_float, fp, C.c_int64, fp,
                                   C.c_int64, C.c_float, fp, C.c_int64, fp, C.c_int64, C.c_int]
+        L.oracle_gemm_f16acc.restype = None
+        L.oracle_gemm_f16acc.argtypes = [C.c_int, C.c_int, C.c_int64, C.c_int64, C.c_int64, C.c_float, fp, C.c_int64, fp,
+                                         C.c_int64, C.c_float, fp, C.c_int64, fp, C.c_int64, C.c_int]
         L.oracle_wmma_unit.restype = None
         L.oracle_wmma_unit.argtypes = [C.c_int] * 8 + [C.c_float, C.c_int, C.c_float, fp, fp, fp, fp]
         _lib = L
@@ -159,6 +162,20 @@ def gemm_ref_f16acc(transA: bool, transB: bool, alpha: float, A16: np.ndarray, B
     if C16 is not None and beta != 0.0:
         D = D + np.float32(beta) * C16.astype(np.float32)
     return np.asfortranarray(D.astype(np.float16))
+
+
+def gemm_c_f16acc(transA: bool, transB: bool, alpha: float, A: np.ndarray, B: np.ndarray, beta: float, Cm, block: int = 16):
+    """The triple loop of oracle.c with a binary16 accumulator (oracle_gemm_f16acc): the second statement
+    ``gemm_ref_f16acc`` is checked against.  Operands as for ``gemm_c``; returns float32 holding binary16 values."""
+    A = np.asfortranarray(A, dtype=np.float32)
+    B = np.asfortranarray(B, dtype=np.float32)
+    M, K = (A.shape[1], A.shape[0]) if transA else A.shape
+    N = B.shape[0] if transB else B.shape[1]
+    D = np.zeros((M, N), dtype=np.float32, order="F")
+    Cf = np.asfortranarray(Cm, dtype=np.float32) if Cm is not None else D
+    clib().oracle_gemm_f16acc(int(transA), int(transB), M, N, K, alpha, _fptr(A), A.shape[0], _fptr(B), B.shape[0],
+                              beta if Cm is not None else 0.0, _fptr(Cf), M, _fptr(D), M, block)
+    return D
 
 
 def errors(D: np.ndarray, ref: np.ndarray) -> tuple[float, float]:

@@ -54,6 +54,27 @@ def test_sgemm_statement_matches_triple_loop(oracle, pkg, tA, tB):
     assert np.all(np.isfinite(d0))
 
 
+@pytest.mark.parametrize("tA,tB", [(False, False), (True, True)])
+def test_float16_accumulating_statements_agree(oracle, pkg, tA, tB):
+    """The two statements of the product with a binary16 accumulator (numpy per 16-wide block, C triple
+    loop) differ only where the sum inside a block lands within rounding distance of a binary16 tie:
+    at most one binary16 ulp on a handful of elements, and both are measurably further from the binary32
+    product than one rounding of it is (so they do state binary16 accumulation)."""
+    rng = pkg.rng
+    M, N, K = 40, 24, 1000  # K is not a multiple of the block
+    a = np.abs(rng.matrix(6, 0, *((K, M) if tA else (M, K)), rng.NORMAL, 1.0, np.float16)) * np.float16(0.25)
+    b = np.abs(rng.matrix(6, 1, *((N, K) if tB else (K, N)), rng.NORMAL, 1.0, np.float16)) * np.float16(0.25)
+    c = rng.matrix(6, 2, M, N, rng.UNIFORM, 1.0, np.float16)
+    blocked = oracle.gemm_ref_f16acc(tA, tB, 1.0, a, b, 0.5, c).astype(np.float32)
+    loop = oracle.gemm_c_f16acc(tA, tB, 1.0, a.astype(np.float32), b.astype(np.float32), 0.5, c.astype(np.float32))
+    ulp = np.spacing(np.abs(loop).astype(np.float16)).astype(np.float32)
+    assert np.all(np.abs(blocked - loop) <= ulp) and np.mean(blocked != loop) < 0.05
+    ref32 = oracle.gemm_ref(tA, tB, 1.0, a, b, 0.5, c.astype(np.float32))
+    once = ref32.astype(np.float16).astype(np.float32)
+    assert oracle.errors(loop, ref32)[0] > 1.5 * oracle.errors(once, ref32)[0]
+    assert oracle.errors(loop, ref32)[0] < 5e-3
+
+
 def test_unit_oracle_follows_the_reference_formula(oracle, pkg):
     """alpha * new_a * new_b + beta * new_c with row-major meaning transpose
     (test/device/wmma.jl:233-246), alpha folded into Float16 A, beta into C in C's type."""
